@@ -5,9 +5,11 @@ The reference keeps contiguous per-sequence buffers (crates/engine/src/flint.rs:
 its sliding layers, a ring of 8192 rows (:26-28, :855-859); its only paging is virtual-memory
 growth in the other model's path (crates/cuda/kernels/vmm.cu:31-70).  Here:
 
-* a group is "full" (a request holds pages for every position) or "sliding" with a window W (a
+* a group is "full" (a request holds pages for every position), "sliding" with a window W (a
   request holds pages only for positions a later query can still see: after a step that leaves
-  the request at length n, blocks that lie wholly below n - W + 1 go back to the pool);
+  the request at length n, blocks that lie wholly below n - W + 1 go back to the pool), or
+  "chunked" with a chunk size C (a query sees only its own chunk of C positions, chunks counted
+  from position 0: blocks that lie wholly below floor(n / C) * C go back to the pool);
 * each group has its own pool and its own block table per request; a table lists the page of
   every logical block (position // page_size), -1 where none is held;
 * pools are LIFO, so a page that was just given back is the next one handed out;
@@ -33,14 +35,22 @@ class OutOfSlots(RuntimeError):
 
 @dataclass(frozen=True)
 class GroupSpec:
-    kind: str                      # "full" | "sliding"
-    window: Optional[int] = None   # sliding: number of visible keys including the query's own position
+    kind: str                      # "full" | "sliding" | "chunked"
+    window: Optional[int] = None   # sliding: number of visible keys including the query's own position; chunked: the chunk size
 
     def __post_init__(self):
-        if self.kind not in ("full", "sliding"):
+        if self.kind not in ("full", "sliding", "chunked"):
             raise ValueError(f"unknown cache group kind {self.kind!r}")
-        if self.kind == "sliding" and not (isinstance(self.window, int) and self.window > 0):
-            raise ValueError("a sliding group needs a positive window")
+        if self.kind != "full" and not (isinstance(self.window, int) and self.window > 0):
+            raise ValueError(f"a {self.kind} group needs a positive window")
+
+    def first_visible(self, position: int) -> int:
+        """The first position a query at `position` can see."""
+        if self.kind == "sliding":
+            return max(0, position - self.window + 1)
+        if self.kind == "chunked":
+            return position // self.window * self.window
+        return 0
 
 
 class PagePool:
@@ -189,10 +199,7 @@ class CacheManager:
     # ------------------------------------------------------------------ pages for a step
     def _first_needed_block(self, g: int, start: int) -> int:
         """First logical block a step whose first new position is `start` reads in group g."""
-        spec = self.groups[g]
-        if spec.kind == "full":
-            return 0
-        return max(0, start - spec.window + 1) // self.page_size
+        return self.groups[g].first_visible(start) // self.page_size
 
     def pages_needed(self, rid: Hashable, n_new: int) -> List[int]:
         """Pages each group's pool must supply so that the request can run n_new more tokens.
@@ -241,10 +248,10 @@ class CacheManager:
         req.length += req.reserved
         req.reserved = 0
         for g, spec in enumerate(self.groups):
-            if spec.kind != "sliding":
+            if spec.kind == "full":
                 continue
-            # the next query sits at position `length` and sees keys > length - window
-            dead = max(0, req.length - spec.window + 1) // self.page_size     # blocks [0, dead) lie wholly below
+            # the next query sits at position `length`; blocks wholly below the first key it sees are dead
+            dead = spec.first_visible(req.length) // self.page_size     # blocks [0, dead) lie wholly below
             table = req.tables[g]
             for b in range(table.first_held, min(dead, len(table))):
                 self.pools[g].give_back(int(table.buf[b]), rid)

@@ -148,7 +148,7 @@ class NativeCacheManager:
         self.groups = list(groups)
         self.page_size = page_size
         lib = host_lib()
-        sliding = i32([g.kind == "sliding" for g in groups])
+        sliding = i32([{"full": 0, "sliding": 1, "chunked": 2}[g.kind] for g in groups])
         windows = i32([g.window or 0 for g in groups])
         pages = i32(list(num_pages))
         self._h = lib.q6k_cm_create(len(groups), ptr32(sliding), ptr32(windows), page_size, ptr32(pages), max_requests)

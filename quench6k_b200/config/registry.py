@@ -54,8 +54,11 @@ def read_config_dict(path: str) -> Dict[str, Any]:
 
 def architecture_of(config_dict: Dict[str, Any]) -> Architecture:
     names = config_dict.get("architectures")
+    if isinstance(config_dict.get("architecture"), str):          # the key some configurations use: one name, no list
+        names = [config_dict["architecture"]]
     if not names or not isinstance(names, list):
-        raise UnknownArchitecture("config.json has no 'architectures' list; registered: " + ", ".join(known_architectures()))
+        raise UnknownArchitecture("config.json names no architecture ('architectures' list or 'architecture'); registered: "
+                                  + ", ".join(known_architectures()))
     return get_architecture(names[0])
 
 

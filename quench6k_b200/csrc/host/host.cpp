@@ -89,8 +89,14 @@ struct CacheRequest {
 };
 
 struct Group {
-    int sliding = 0;                     // 0: a request holds pages for every position; 1: only for the last `window`
-    int window = 0;
+    int sliding = 0;                     // 0: a request holds pages for every position; 1: only for the last `window`;
+    int window = 0;                      // 2: only for the query's own chunk of `window` positions (chunks counted from 0)
+    // The first position a query at `position` can see.
+    int64_t first_visible(int64_t position) const {
+        if (sliding == 1) return position - window + 1 < 0 ? 0 : position - window + 1;
+        if (sliding == 2) return position / window * window;
+        return 0;
+    }
 };
 
 // Keys and values in pages with a block table per request and group; a sliding group gives pages
@@ -108,9 +114,7 @@ struct CacheManager {
         return it == requests.end() ? nullptr : &it->second;
     }
     int first_needed_block(int g, int64_t start) const {
-        if (!groups[g].sliding) return 0;
-        const int64_t lo = start - groups[g].window + 1;
-        return (int)((lo < 0 ? 0 : lo) / page_size);
+        return (int)(groups[g].first_visible(start) / page_size);
     }
     int add(int64_t id, int* slot) {
         if (requests.count(id)) return fail(E_KEY, "request %lld is already live", (long long)id);
@@ -172,7 +176,7 @@ struct CacheManager {
         for (size_t g = 0; g < groups.size(); ++g)
             if (need[g] > pools[g].num_free())
                 return fail(E_PAGES, "group %d (%s) needs %d pages for request %lld, %d are free", (int)g,
-                            groups[g].sliding ? "sliding" : "full", need[g], (long long)id, pools[g].num_free());
+                            groups[g].sliding == 1 ? "sliding" : groups[g].sliding == 2 ? "chunked" : "full", need[g], (long long)id, pools[g].num_free());
         for (size_t g = 0; g < groups.size(); ++g)
             for (int i = 0; i < need[g]; ++i) r->tables[g].pages.push_back(pools[g].take(id));
         r->reserved = n_new;
@@ -185,10 +189,9 @@ struct CacheManager {
         r->reserved = 0;
         for (size_t g = 0; g < groups.size(); ++g) {
             if (!groups[g].sliding) continue;
-            // the next query sits at position `length` and sees keys > length - window
-            const int64_t lo = r->length - groups[g].window + 1;
+            // the next query sits at position `length`; blocks wholly below the first key it sees are dead
             BlockTable& t = r->tables[g];
-            int dead = (int)((lo < 0 ? 0 : lo) / page_size);
+            int dead = (int)(groups[g].first_visible(r->length) / page_size);
             if (dead > (int)t.pages.size()) dead = (int)t.pages.size();
             for (int b = t.first_held; b < dead; ++b) {
                 if (int rc = pools[g].give_back(t.pages[b], id)) return rc;
@@ -458,7 +461,7 @@ API void* q6k_cm_create(int n_groups, const int* sliding, const int* windows, in
     cm->page_size = page_size;
     for (int g = 0; g < n_groups; ++g) {
         if (sliding[g] && windows[g] <= 0) {
-            fail(E_VALUE, "a sliding group needs a positive window");
+            fail(E_VALUE, "a sliding or chunked group needs a positive window");
             delete cm;
             return nullptr;
         }

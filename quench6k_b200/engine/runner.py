@@ -69,8 +69,10 @@ class ModelRunner:
                 g = self.group_of[p]
                 # head-major: a head's pages are contiguous; one page beyond the manager's pool takes what filler entries write
                 lead, dt = (r.kv_heads, pages[g] + 1, page_size), r.dtype or rt.dtype
-                self.caches.append(LayerCache(g, torch.zeros((*lead, r.head_dim), dtype=dt, device=rt.device),
-                                              torch.zeros((*lead, r.v_dim or r.head_dim), dtype=dt, device=rt.device), page_size))
+                k = torch.zeros((*lead, r.head_dim), dtype=dt, device=rt.device)
+                # values that are the first entries of the key rows get no pages of their own: a view into the keys'
+                v = k[..., :r.v_dim] if r.values_in_keys else torch.zeros((*lead, r.v_dim or r.head_dim), dtype=dt, device=rt.device)
+                self.caches.append(LayerCache(g, k, v, page_size))
 
         def state_for(s):
             """One tensor [slots + 1, *shape] per declared state (the extra slot is the filler entries')."""

@@ -105,7 +105,7 @@ def capacity_tokens(manager) -> int:
     """Most tokens one request can ever hold: the smallest pool of a group that keeps every key
     bounds it.  A sliding group holds a window's worth of pages whatever the length, so its
     (possibly much smaller) pool bounds nothing."""
-    full = [p.num_pages for p, g in zip(manager.pools, manager.groups) if g.kind != "sliding"]
+    full = [p.num_pages for p, g in zip(manager.pools, manager.groups) if g.kind == "full"]
     return min(full) * manager.page_size if full else 1 << 60
 
 
@@ -113,7 +113,7 @@ def check_pools(manager) -> None:
     """A sliding group must hold its window and one more token wherever they lie on the pages,
     or no request could ever advance."""
     for i, (p, g) in enumerate(zip(manager.pools, manager.groups)):
-        if g.kind == "sliding":
+        if g.kind != "full":
             need = -(-g.window // manager.page_size) + 1
             if p.num_pages < need:
                 raise ValueError(f"cache group {i}: {p.num_pages} pages cannot hold a window of {g.window} keys and the next token "

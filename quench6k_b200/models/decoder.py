@@ -13,11 +13,9 @@ import torch
 
 from .. import ops
 from ..parts import linear
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheRequest, LayerCache, Runtime, make_part,
+from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheRequest, LayerCache, Runtime, WeightedRows, make_part,
                           to_operand)
 from ..spec import ModelSpec, TensorSpec
-
-_SUB = {"norm1": "input_layernorm.", "mixer": "self_attn.", "norm2": "post_attention_layernorm.", "ffn": "mlp."}
 
 
 class DecoderModel:
@@ -29,15 +27,23 @@ class DecoderModel:
             if ls.block not in BLOCKS:
                 raise KeyError(f"unknown block arrangement {ls.block!r}; registered: {', '.join(sorted(BLOCKS))}")
             norm1 = make_part(NORMS, "norm", ls.norm, size=D)
-            norm2 = make_part(NORMS, "norm", ls.norm, size=D)
             mixer = make_part(MIXERS, "mixer", ls.mixer, hidden_size=D)
-            ffn = make_part(FEED_FORWARDS, "feed-forward", ls.ffn, hidden_size=D)
-            self.blocks.append(BLOCKS[ls.block](norm1, mixer, norm2, ffn))
+            ffn = make_part(FEED_FORWARDS, "feed-forward", ls.ffn, hidden_size=D) if ls.ffn is not None else None
+            norm2 = make_part(NORMS, "norm", ls.norm, size=D) if ffn is not None else None
+            after = {}
+            if ls.post_norm is not None:
+                after["norm1b"] = make_part(NORMS, "norm", ls.post_norm, size=D)
+                if ffn is not None:
+                    after["norm2b"] = make_part(NORMS, "norm", ls.post_norm, size=D)
+            self.blocks.append(BLOCKS[ls.block](norm1, mixer, norm2, ffn, **after))
         self.final_norm = make_part(NORMS, "norm", spec.final_norm, size=D)
         self.order = list(spec.order)
         self.kv_source = list(spec.kv_source)
         if len(self.kv_source) != len(self.order):
             raise ValueError("kv_source and order differ in length")
+        self.readd = set(spec.readd_embedding)
+        if any(not 0 < p < len(self.order) for p in self.readd):
+            raise ValueError("readd_embedding names a position outside 1..executed layers - 1")
         self.rt: Optional[Runtime] = None
 
     # ------------------------------------------------------------------ declaration
@@ -45,8 +51,8 @@ class DecoderModel:
         s = self.spec
         out = [TensorSpec(s.embed_name, (s.vocab_size, s.hidden_size))]
         for ls, b in zip(s.layers, self.blocks):
-            for sub, part in (("norm1", b.norm1), ("mixer", b.mixer), ("norm2", b.norm2), ("ffn", b.ffn)):
-                out += [TensorSpec(ls.prefix + _SUB[sub] + t.name, t.shape, t.role, t.init) for t in part.tensors()]
+            for sub, part in b.parts():
+                out += [TensorSpec(ls.prefix + s.sub_names[sub] + t.name, t.shape, t.role, t.init) for t in part.tensors()]
         out += [TensorSpec(s.final_norm_prefix + t.name, t.shape, t.role, t.init) for t in self.final_norm.tensors()]
         if s.head_name is not None:
             out.append(TensorSpec(s.head_name, (s.vocab_size, s.hidden_size)))
@@ -67,7 +73,7 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         parts = [self.final_norm]
         for b in self.blocks:
-            parts += [b.norm1, b.mixer, b.norm2, b.ffn]
+            parts += [part for _, part in b.parts()]
         return all(getattr(x, "graph_safe", False) for x in parts)
 
     # ------------------------------------------------------------------ weights
@@ -76,8 +82,8 @@ class DecoderModel:
         self.rt = rt
         self.embed = to_operand(get(s.embed_name), rt)
         for ls, b in zip(s.layers, self.blocks):
-            for sub, part in (("norm1", b.norm1), ("mixer", b.mixer), ("norm2", b.norm2), ("ffn", b.ffn)):
-                pre = ls.prefix + _SUB[sub]
+            for sub, part in b.parts():
+                pre = ls.prefix + s.sub_names[sub]
                 part.bind(lambda n, pre=pre: get(pre + n), rt)
         self.final_norm.bind(lambda n: get(s.final_norm_prefix + n), rt)
         self.head = self.embed if s.head_name is None else to_operand(get(s.head_name), rt)
@@ -88,13 +94,25 @@ class DecoderModel:
         [len(ctx.logit_rows), vocab] or None when no row is wanted."""
         ops.current_tag = "embedding"
         h = ops.embed(ctx.token_ids, self.embed, fed=ctx.fed)
+        h0 = h.clone() if self.readd else None      # the embedding output, for the passes of a repeated span that take it again
         pending = None                      # an add into h that a block has left to the next norm
         for p, i in enumerate(self.order):
             ctx.position = p
-            pending = self.blocks[i].forward(h, ctx, caches[p], states[p], pending)
+            block = self.blocks[i]
+            if p in self.readd:
+                if block.takes_extra:
+                    pending = block.forward(h, ctx, caches[p], states[p], pending, extra=h0)
+                    continue
+                if pending is not None:
+                    pending.apply(h)
+                    pending = None
+                h += h0
+            pending = block.forward(h, ctx, caches[p], states[p], pending)
         if ctx.n_logit_rows == 0:
             return None
-        if pending is not None and not self.final_norm.fuses_weighted_rows:
+        # an add that is left: the last norm makes it if it can (it normalises picked rows only, so a sublayer result that
+        # passes a norm of its own is added first, for all rows)
+        if pending is not None and not (isinstance(pending, WeightedRows) and self.final_norm.fuses_weighted_rows):
             pending.apply(h)
             pending = None
         ops.current_tag = "norm.final"

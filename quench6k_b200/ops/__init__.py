@@ -955,3 +955,188 @@ def topk_pool(logits: torch.Tensor, k: int):
     vals = torch.empty((rows, k), dtype=torch.float32, device=logits.device)
     _call("q6k_topk_pool", _ptr(logits), _i(rows), _i(V), _i(k), _ptr(ids), _ptr(vals), _stream())
     return ids, vals
+
+
+# --------------------------------------------------------------------------- layer norm, selective scan, flexible attention
+def layernorm(h: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+              rows: Optional[torch.Tensor] = None, after=None, extra: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """Layer norm with weight and bias on the FP32 stream h [T, D], up to three steps in one pass over each row:
+    after = (y, wa, ba): h += LN(y; wa, ba) first (y FP32 [T, D] or [slices, T, D] partial sums added in order);
+    extra (FP32 like h): h += extra next; w, b: the result LN(h; w, b) in out_dtype (None: no result, h is only
+    updated).  rows: int32 row numbers to normalise (without after and extra)."""
+    _need(h, "h", torch.float32)
+    T, D = h.shape
+    R = T if rows is None else rows.numel()
+    y = wa = ba = None
+    splits, stride = 1, 0
+    if after is not None:
+        y, wa, ba = after
+        _need(y, "y", torch.float32)
+        _need(wa, "wa", torch.float32, (D,))
+        _need(ba, "ba", torch.float32, (D,))
+        if y.dim() == 3:
+            splits, stride = y.shape[0], y.shape[1] * y.shape[2]
+        if tuple(y.shape[-2:]) != (T, D):
+            raise KernelError("layernorm: the sublayer's result does not match h")
+    if extra is not None:
+        _need(extra, "extra", torch.float32, (T, D))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if after is not None or extra is not None:
+            raise KernelError("layernorm: picked rows are only normalised")
+    out = None
+    if w is not None:
+        _need(w, "w", torch.float32, (D,))
+        _need(b, "b", torch.float32, (D,))
+        out = torch.empty((R, D), dtype=out_dtype, device=h.device)
+    _call("q6k_layernorm", _ptr(h), _ptr(y), _i(splits), _ll(stride), _ptr(wa), _ptr(ba), _ptr(extra), _ptr(w), _ptr(b), _ptr(rows),
+          _ptr(out), _i(R), _i(D), _f(eps), _i(dtype_code(out_dtype)), _stream())
+    return out
+
+
+def conv_silu(x: torch.Tensor, channels: int, w: torch.Tensor, bias: torch.Tensor, tail: torch.Tensor, req_of_token: torch.Tensor,
+              q_start: torch.Tensor, slot_ids: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """out[t, c] = out_dtype(silu(bias[c] + sum_k w[c, k] * x[t - (taps-1-k), c])) per request; inputs before a portion
+    come from tail [slots, taps-1, C] (the last inputs of the request's earlier portions, zeros at its start)."""
+    _need(x, "x", torch.float32)
+    T = x.shape[0]
+    taps = w.shape[1]
+    _need(w, "w", torch.float32, (channels, taps))
+    _need(bias, "bias", torch.float32, (channels,))
+    _need(tail, "tail", torch.float32)
+    if tuple(tail.shape[1:]) != (max(taps - 1, 0), channels) or x.shape[1] < channels:
+        raise KernelError("conv_silu: shapes disagree")
+    out = torch.empty((T, channels), dtype=out_dtype, device=x.device)
+    _call("q6k_conv_silu", _ptr(x), _i(x.stride(0)), _ptr(w), _ptr(bias), _ptr(tail), _ptr(req_of_token), _ptr(q_start), _ptr(slot_ids),
+          _ptr(out), _i(T), _i(channels), _i(taps), _i(dtype_code(out_dtype)), _stream())
+    return out
+
+
+def cast_columns(src: torch.Tensor, col0: int, n: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """out_dtype(src[:, col0:col0 + n]) as a contiguous matrix."""
+    _need(src, "src", torch.float32)
+    out = torch.empty((src.shape[0], n), dtype=out_dtype, device=src.device)
+    _call("q6k_cast_columns", _ptr(src), _i(src.stride(0)), _i(col0), _i(n), _ptr(out), _i(src.shape[0]), _i(dtype_code(out_dtype)), _stream())
+    return out
+
+
+def selective_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, proj: torch.Tensor, b_col: int, c_col: int,
+                   A: torch.Tensor, D: torch.Tensor, xz: torch.Tensor, z_col: int, state: torch.Tensor, tail: torch.Tensor,
+                   q_start: torch.Tensor, slot_ids: torch.Tensor, R: int) -> torch.Tensor:
+    """The selective-scan recurrence over each request's tokens in order, from and into the request's state slot:
+    dt = softplus(dt_raw + dt_bias); S <- exp(dt A) S + dt u B; y = (S . C + D u) * silu(z).  u [T, C] (operand dtype),
+    dt_raw FP32 [T, C], proj FP32 [T, *] holding B and C (N columns each from b_col, c_col), A FP32 [C, N], xz FP32 [T, *]
+    holding the convolution's inputs (columns 0..) and z (columns z_col..), state FP32 [slots, C, N], tail FP32
+    [slots, taps-1, C] (moved on to the portion's end).  Returns [T, C] in u's dtype."""
+    _need(u, "u")
+    T, C = u.shape
+    N = A.shape[1]
+    _need(dt_raw, "dt_raw", torch.float32, (T, C))
+    _need(dt_bias, "dt_bias", torch.float32, (C,))
+    _need(proj, "proj", torch.float32)
+    _need(A, "A", torch.float32, (C, N))
+    _need(D, "D", torch.float32, (C,))
+    _need(xz, "xz", torch.float32)
+    _need(state, "state", torch.float32)
+    _need(tail, "tail", torch.float32)
+    taps = tail.shape[1] + 1
+    if tuple(state.shape[1:]) != (C, N) or tail.shape[2] != C or tail.shape[0] != state.shape[0]:
+        raise KernelError("selective_scan: state shapes disagree")
+    out = torch.empty((T, C), dtype=u.dtype, device=u.device)
+    _call("q6k_selective_scan", _ptr(u), _ptr(dt_raw), _ptr(dt_bias), _ptr(proj), _i(proj.stride(0)), _i(b_col), _i(c_col), _ptr(A), _ptr(D),
+          _ptr(xz), _i(xz.stride(0)), _i(z_col), _ptr(state), _ptr(tail), _ptr(q_start), _ptr(slot_ids), _ptr(out), _i(R), _i(C), _i(N),
+          _i(taps), _i(dtype_code(u.dtype)), _stream())
+    return out
+
+
+def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_norm, eps: float, rotary, positions: torch.Tensor,
+              req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int, k_pages: Optional[torch.Tensor],
+              v_pages: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """qk_prep for keys and values of different widths: qkv FP32 [T, Hq hd + Hkv hd + Hkv vd] (or split-K slices of it);
+    q -> [T, Hq, hd]; k -> pages [Hkv, P, page, hd]; v -> pages [Hkv, P, page, vd]."""
+    _need(qkv, "qkv", torch.float32)
+    splits, split_stride = 1, 0
+    if qkv.dim() == 3:
+        splits, split_stride = qkv.shape[0], qkv.shape[1] * qkv.shape[2]
+        qkv = qkv[0]
+    T = qkv.shape[0]
+    write = k_pages is not None
+    if write:
+        _need(k_pages, "k_pages", out_dtype)
+        _need(v_pages, "v_pages", out_dtype)
+        _need(block_table, "block_table", torch.int32)
+        if tuple(k_pages.shape[2:]) != (page_size, hd) or tuple(v_pages.shape[2:]) != (page_size, vd) or k_pages.shape[0] != Hkv:
+            raise KernelError("qkv_pages: the pages do not match the heads")
+    if qkv.shape[1] < Hq * hd + (Hkv * (hd + vd) if write else 0):
+        raise KernelError("qkv_pages: qkv rows are too short")
+    inv_freq, rotary_dim, neighbours = rotary if rotary is not None else (None, 0, False)
+    q = torch.empty((T, Hq, hd), dtype=out_dtype, device=qkv.device)
+    _call("q6k_qkv_pages", _ptr(qkv), _i(qkv.stride(0)), _i(splits), _ll(split_stride), _i(T), _i(Hq), _i(Hkv), _i(hd), _i(vd), _ptr(q_norm),
+          _ptr(k_norm), _f(eps), _ptr(inv_freq), _i(rotary_dim), _i(1 if neighbours else 0), _ptr(positions), _ptr(req_of_token),
+          _ptr(block_table), _i(block_table.shape[1] if block_table is not None else 1), _i(page_size),
+          _i(k_pages.shape[1] if write else 0), _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(1 if write else 0),
+          _i(dtype_code(out_dtype)), _stream())
+    return q
+
+
+def latent_prep(x: torch.Tensor, H: int, dim: int, rd: int, rank: int, c_weight: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor],
+                turn: int, positions: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                pages: torch.Tensor):
+    """x FP32 [T, H (dim + rd) + rank + rd] -> (qn [H, T, dim], qr [H, T, rd]) in the pages' dtype, and the token's row
+    [RMS-normed latent | rotated shared key part] into pages [1, P, page, rank + rd]."""
+    _need(x, "x", torch.float32)
+    T = x.shape[0]
+    if x.shape[1] < H * (dim + rd) + rank + rd or tuple(pages.shape[2:]) != (page_size, rank + rd) or pages.shape[0] != 1:
+        raise KernelError("latent_prep: shapes disagree")
+    _need(pages, "pages")
+    _need(c_weight, "c_weight", torch.float32, (rank,))
+    qn = torch.empty((H, T, dim), dtype=pages.dtype, device=x.device)
+    qr = torch.empty((H, T, rd), dtype=pages.dtype, device=x.device)
+    _call("q6k_latent_prep", _ptr(x), _i(x.stride(0)), _i(T), _i(H), _i(dim), _i(rd), _i(rank), _ptr(c_weight), _f(eps), _ptr(inv_freq),
+          _i(turn), _ptr(positions), _ptr(req_of_token), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _ptr(qn), _ptr(qr),
+          _ptr(pages), _i(dtype_code(pages.dtype)), _stream())
+    return qn, qr
+
+
+def heads_to_rows(src: torch.Tensor, H: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """FP32 [H * T, n] (head-major) -> out_dtype [T, H * n]."""
+    _need(src, "src", torch.float32)
+    T, n = src.shape[0] // H, src.shape[1]
+    out = torch.empty((T, H * n), dtype=out_dtype, device=src.device)
+    _call("q6k_heads_to_rows", _ptr(src), _ptr(out), _i(H), _i(T), _i(n), _i(dtype_code(out_dtype)), _stream())
+    return out
+
+
+def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], head_major: bool, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                   block_table: torch.Tensor, req_of_token: torch.Tensor, positions: torch.Tensor, H: int, scale: float,
+                   window: Optional[int] = None, chunk: Optional[int] = None, talk: Optional[torch.Tensor] = None,
+                   out_head_major: bool = False) -> torch.Tensor:
+    """Causal attention of every row over its request's pages, for any key and value widths.  A query row is the FP32
+    part q_f32 [H*T or T*H rows, da] followed by q [rows, db] in the pages' dtype (either may be None); rows are head-major
+    (h T + t) or token-major.  k_pages [Hkv, P, page, dk]; v_pages [Hkv, P, page, dv], possibly a view into k_pages (the
+    last axis contiguous, the others with k's strides).  window: only the last `window` keys; chunk: only keys of the
+    position's own block of `chunk` positions; talk FP32 [H, H]: the heads' softmax weights are mixed by it before the
+    values.  Returns [H, T, dv] (out_head_major) or [T, H dv]."""
+    da = q_f32.shape[-1] if q_f32 is not None else 0
+    db = q.shape[-1] if q is not None else 0
+    rows = (q_f32 if q_f32 is not None else q).numel() // (da if q_f32 is not None else db)
+    T = rows // H
+    if q_f32 is not None:
+        _need(q_f32, "q_f32", torch.float32)
+    if q is not None:
+        _need(q, "q", k_pages.dtype)
+    Hkv, num_pages, page_size, dk = k_pages.shape
+    dv = v_pages.shape[-1]
+    if da + db != dk or v_pages.dtype != k_pages.dtype or tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]):
+        raise KernelError(f"attention_flex: a query of {da}+{db} against pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)}")
+    for nm, p in (("k_pages", k_pages), ("v_pages", v_pages)):
+        if not p.is_cuda or p.stride(3) != 1 or p.stride(1) != page_size * p.stride(2):
+            raise KernelError(f"attention_flex: {nm} has strides {p.stride()}")
+    if talk is not None:
+        _need(talk, "talk", torch.float32, (H, H))
+    out = torch.empty((H, T, dv) if out_head_major else (T, H * dv), dtype=k_pages.dtype, device=k_pages.device)
+    _call("q6k_attention_flex", _ptr(q_f32), _i(da), _ptr(q), _i(db), _i(1 if head_major else 0), _ptr(k_pages), _ll(k_pages.stride(0)),
+          _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv), _ptr(block_table),
+          _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _i(window or 0), _i(chunk or 0), _f(scale),
+          _ptr(talk), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv), _i(dtype_code(k_pages.dtype)), _stream())
+    return out

@@ -1,6 +1,11 @@
 """Grouped-query self-attention over the paged cache, with optional per-head QK-norm, learned
 sinks and a sliding window (reference: crates/engine/src/flint.rs:815-913 for the order of
-operations, crates/cuda/kernels/flint.cu:125-173 and :211-561 for the arithmetic)."""
+operations, crates/cuda/kernels/flint.cu:125-173 and :211-561 for the arithmetic).
+
+Beyond the reference: values of another width than the keys (v_dim), a given score scale, a mask of chunks (a position
+sees the earlier positions of its own block of `chunk` positions, blocks counted from position 0), and the heads'
+softmax weights mixed by a learned [heads, heads] matrix before they meet the values (`talk`).  Layers that use any of
+these run the flexible attention kernels; the others run as before."""
 from __future__ import annotations
 
 import math
@@ -20,26 +25,42 @@ class Attention(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, eps: float,
                  pos: PartSpec, window: Optional[int] = None, sinks: bool = False, qk_norm: bool = False,
-                 norm_init: str = "ones", sink_std: float = 1.0):
+                 norm_init: str = "ones", sink_std: float = 1.0, v_dim: Optional[int] = None, scale: Optional[float] = None,
+                 chunk: Optional[int] = None, talk: bool = False, names=None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
         self.D, self.Hq, self.Hkv, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
+        self.vd = int(v_dim) if v_dim else head_dim
         self.eps, self.window, self.has_sinks, self.qk_norm = float(eps), window, sinks, qk_norm
+        self.chunk, self.talk = (int(chunk) if chunk else None), bool(talk)
         self.norm_init, self.sink_std = norm_init, sink_std
         self.pos = make_part(POSITION_ENCODINGS, "position encoding", pos)
-        self.scale = 1.0 / math.sqrt(head_dim)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        # the flexible kernels: any widths, chunks, mixed heads; the fixed-shape kernels: everything the reference has
+        self.flexible = self.vd != head_dim or self.chunk is not None or self.talk
+        if self.flexible and sinks:
+            raise ValueError("sinks are not combined with chunks, mixed heads or values of another width")
+        if self.flexible and self.pos.rotary_table() is None and not self.pos.is_identity:
+            raise ValueError("the flexible attention kernels take a rotation of pairs or no position encoding")
+        if self.talk and (num_heads > 64 or self.vd > 256):
+            raise ValueError(f"mixed heads: at most 64 heads and values up to 256 wide, not {num_heads} and {self.vd}")
+        if not self.flexible and (head_dim % 16 or head_dim > 256):
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+        # the tensors' names relative to the part's prefix (an architecture may call them anything)
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "q_norm": "q_norm.weight",
+                      "k_norm": "k_norm.weight", "sinks": "sinks", "talk": "talk.weight", **(names or {})}
 
     def tensors(self):
-        D, Hq, Hkv, hd = self.D, self.Hq, self.Hkv, self.hd
-        out = [TensorSpec("q_proj.weight", (Hq * hd, D)), TensorSpec("k_proj.weight", (Hkv * hd, D)),
-               TensorSpec("v_proj.weight", (Hkv * hd, D)), TensorSpec("o_proj.weight", (D, Hq * hd))]
+        D, Hq, Hkv, hd, n = self.D, self.Hq, self.Hkv, self.hd, self.names
+        out = [TensorSpec(n["q"], (Hq * hd, D)), TensorSpec(n["k"], (Hkv * hd, D)),
+               TensorSpec(n["v"], (Hkv * self.vd, D)), TensorSpec(n["o"], (D, Hq * self.vd))]
         if self.qk_norm:
             init = ("ones",) if self.norm_init == "ones" else ("ones_plus", 0.1)
-            out += [TensorSpec("q_norm.weight", (hd,), "f32", init), TensorSpec("k_norm.weight", (hd,), "f32", init)]
+            out += [TensorSpec(n["q_norm"], (hd,), "f32", init), TensorSpec(n["k_norm"], (hd,), "f32", init)]
         if self.has_sinks:
-            out.append(TensorSpec("sinks", (Hq,), "f32", ("normal", self.sink_std)))
+            out.append(TensorSpec(n["sinks"], (Hq,), "f32", ("normal", self.sink_std)))
+        if self.talk:
+            out.append(TensorSpec(n["talk"], (Hq, Hq), "f32", ("normal", 0.5)))
         out += [TensorSpec("position." + t.name, t.shape, t.role, t.init) for t in self.pos.tensors()]
         return out
 
@@ -47,23 +68,45 @@ class Attention(Mixer):
         self.rt = rt
         # q, k and v rows stacked so one product yields [q | k | v] per token: each piece is copied into its place
         # on the device as it arrives, so that no two copies of the three are held at once
-        nq, nk = self.Hq * self.hd, self.Hkv * self.hd
-        self.w_qkv = torch.empty((nq + 2 * nk, self.D), dtype=rt.dtype, device=rt.device)
-        for name, lo, hi in (("q_proj.weight", 0, nq), ("k_proj.weight", nq, nq + nk), ("v_proj.weight", nq + nk, nq + 2 * nk)):
+        nq, nk, nv, n = self.Hq * self.hd, self.Hkv * self.hd, self.Hkv * self.vd, self.names
+        self.w_qkv = torch.empty((nq + nk + nv, self.D), dtype=rt.dtype, device=rt.device)
+        for name, lo, hi in ((n["q"], 0, nq), (n["k"], nq, nq + nk), (n["v"], nq + nk, nq + nk + nv)):
             self.w_qkv[lo:hi].copy_(get(name))
         self.w_q = self.w_qkv[:nq]
-        self.w_o = to_operand(get("o_proj.weight"), rt)
-        self.q_norm = to_f32(get("q_norm.weight"), rt) if self.qk_norm else None
-        self.k_norm = to_f32(get("k_norm.weight"), rt) if self.qk_norm else None
-        self.sinks = to_f32(get("sinks"), rt) if self.has_sinks else None
-        self.pos.bind(lambda n: get("position." + n), rt)
+        self.w_o = to_operand(get(n["o"]), rt)
+        self.q_norm = to_f32(get(n["q_norm"]), rt) if self.qk_norm else None
+        self.k_norm = to_f32(get(n["k_norm"]), rt) if self.qk_norm else None
+        self.sinks = to_f32(get(n["sinks"]), rt) if self.has_sinks else None
+        self.w_talk = to_f32(get(n["talk"]), rt) if self.talk else None
+        self.pos.bind(lambda name: get("position." + name), rt)
 
     def cache_request(self):
+        v = self.vd if self.vd != self.hd else None
+        if self.chunk is not None and (self.window is None or self.window >= self.chunk):
+            return CacheRequest("chunked", self.chunk, self.Hkv, self.hd, v)      # what a chunk's start hides, no later query sees
         if self.window is not None:
-            return CacheRequest("sliding", int(self.window), self.Hkv, self.hd)
-        return CacheRequest("full", None, self.Hkv, self.hd)
+            return CacheRequest("sliding", int(self.window), self.Hkv, self.hd, v)
+        return CacheRequest("full", None, self.Hkv, self.hd, v)
+
+    def _forward_flexible(self, xn, ctx, cache):
+        """Any key and value widths, a window and/or chunks, mixed heads: the flexible kernels."""
+        rt, write = self.rt, cache.write
+        table = ctx.block_tables[cache.group]
+        ops.current_tag = "attention.qkv"
+        qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=True)
+        ops.current_tag = "attention.prepare"
+        q = ops.qkv_pages(qkv, self.Hq, self.Hkv, self.hd, self.vd, self.q_norm, self.k_norm, self.eps, self.pos.rotary_table(),
+                          ctx.positions, ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
+                          cache.v if write else None, rt.dtype)
+        ops.current_tag = "attention.keys"
+        a = ops.attention_flex(None, q.view(-1, self.hd), False, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.Hq,
+                               self.scale, window=self.window, chunk=self.chunk, talk=self.w_talk)
+        ops.current_tag = "attention.o"
+        return linear.matmul(a, self.w_o, rt, partials_ok=True)
 
     def forward(self, xn, ctx, cache, state, out):
+        if self.flexible:
+            return self._forward_flexible(xn, ctx, cache)
         rt = self.rt
         write = cache.write
         # which attention kernels this step takes, and the plan of the key splits, before anything of the layer is

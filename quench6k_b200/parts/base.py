@@ -47,15 +47,17 @@ class Runtime:
 class CacheRequest:
     """What a mixer needs from the cache manager.  Layers with equal requests share a group
     (one block table per request and group)."""
-    kind: str                           # "full": every key; "sliding": the last `window` keys
+    kind: str                           # "full": every key; "sliding": the last `window` keys; "chunked": the keys of the
+                                        # query's own block of `window` positions (blocks counted from position 0)
     window: Optional[int]
     kv_heads: int
     head_dim: int                       # width of a key
     v_dim: Optional[int] = None         # width of a value; None: the key's
     dtype: Optional[torch.dtype] = None  # what the pages hold; None: the runtime's operand dtype
+    values_in_keys: bool = False        # a value is the first v_dim entries of its key row (a cached latent): no pages of its own
 
     def key(self) -> Tuple:
-        return (self.kind, self.window, self.kv_heads, self.head_dim, self.v_dim or self.head_dim, self.dtype)
+        return (self.kind, self.window, self.kv_heads, self.head_dim, self.v_dim or self.head_dim, self.dtype, self.values_in_keys)
 
 
 @dataclass
@@ -102,6 +104,18 @@ class WeightedRows:
         ops.combine(self.y, self.pair_row, self.weights, h)
 
 
+@dataclass
+class PostNormed:
+    """A residual add that has not been made yet: h += norm(y), the closing step of a sublayer whose result passes a norm
+    of its own before it joins the stream.  A block may return it instead of adding, and a norm that understands it
+    (Norm.fuses_post_normed) makes the add in the pass that normalises for the next sublayer."""
+    y: torch.Tensor                       # FP32 [T, D], or [slices, T, D] partial sums to be added in order
+    norm: "Norm"
+
+    def apply(self, h: torch.Tensor) -> None:
+        self.norm.add_normed(h, self.y)
+
+
 class Tap:
     """A debugging aid: a part that is given a Tap copies small per-row results of every forward
     into it (the routed experts: each row's chosen experts and its router logits), one static
@@ -125,6 +139,11 @@ class Tap:
 
 class Norm(Part):
     fuses_weighted_rows = False           # forward(..., add=WeightedRows) is understood
+    fuses_post_normed = False             # forward(..., add=PostNormed) is understood
+
+    def add_normed(self, h: torch.Tensor, y: torch.Tensor) -> None:
+        """h += this norm of y (y FP32 [T, D] or [slices, T, D] partial sums), in place."""
+        raise NotImplementedError
 
     def forward(self, h: torch.Tensor, rows: Optional[torch.Tensor] = None, add=None) -> torch.Tensor:
         """Normalised rows of h in the operand dtype.  `add`: FP32 of h's shape, or [slices, T, D]
@@ -168,8 +187,18 @@ class FeedForward(Part):
 
 
 class Block:
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
+    takes_extra = False                   # forward(..., extra=x) adds x into the stream inside the block's first norm
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward],
+                 norm1b: Optional[Norm] = None, norm2b: Optional[Norm] = None):
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+        self.norm1b, self.norm2b = norm1b, norm2b      # norms of the sublayers' results, in arrangements that have them
+
+    def parts(self):
+        """(role, part) of everything that holds tensors, in the order the tensors are declared."""
+        out = [("norm1", self.norm1), ("mixer", self.mixer), ("norm2", self.norm2), ("ffn", self.ffn),
+               ("norm1b", self.norm1b), ("norm2b", self.norm2b)]
+        return [(k, v) for k, v in out if v is not None]
 
     def forward(self, h, ctx, cache, state, pending=None):
         """Runs the block on the stream h in place.  `pending`: an add into h the block before has

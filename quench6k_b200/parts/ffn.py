@@ -20,23 +20,32 @@ from .base import FeedForward, WeightedRows, register_feed_forward, to_operand
 class DenseSwiGLU(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    def __init__(self, hidden_size: int, intermediate_size: int, names=None):
         self.D, self.I = hidden_size, intermediate_size
+        # the tensors' names relative to the part's prefix (an architecture may call them anything)
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
 
     def tensors(self):
-        return [TensorSpec("gate_proj.weight", (self.I, self.D)), TensorSpec("up_proj.weight", (self.I, self.D)),
-                TensorSpec("down_proj.weight", (self.D, self.I))]
+        n = self.names
+        return [TensorSpec(n["gate"], (self.I, self.D)), TensorSpec(n["up"], (self.I, self.D)), TensorSpec(n["down"], (self.D, self.I))]
 
     def bind(self, get, rt):
         self.rt = rt
-        self.w_gate, self.w_up = to_operand(get("gate_proj.weight"), rt), to_operand(get("up_proj.weight"), rt)
-        self.w_down = to_operand(get("down_proj.weight"), rt)
+        self.w_gate, self.w_up = to_operand(get(self.names["gate"]), rt), to_operand(get(self.names["up"]), rt)
+        self.w_down = to_operand(get(self.names["down"]), rt)
 
     def forward(self, xn, ctx, out):
         ops.current_tag = "dense.gate_up"
         act = linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt)
         ops.current_tag = "dense.down"
         linear.matmul(act, self.w_down, self.rt, out=out, accumulate=True)
+
+    def compute(self, xn, ctx):
+        """The result itself, FP32 [T, D] (or split-K slices of it), for a block whose norm takes it before the stream does."""
+        ops.current_tag = "dense.gate_up"
+        act = linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt)
+        ops.current_tag = "dense.down"
+        return linear.matmul(act, self.w_down, self.rt, partials_ok=True)
 
 
 @register_feed_forward("moe")

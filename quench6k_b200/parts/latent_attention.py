@@ -1,0 +1,79 @@
+"""Attention over a cached latent: per token one low-rank vector c (RMS-normed) and one rotated key part shared by all
+heads are cached; a head's key is [W_uk_h c | rotated part], its value W_uv_h c.  Scores and output are computed in the
+latent space, which needs nothing but the cache: with q_h = [a_h | r_h],
+
+    score_h(i, j) = scale * ((W_uk_h^T a_h(i)) . c(j) + r_h(i) . k_rot(j)),     out_h(i) = W_uv_h (sum_j p_h(i, j) c(j)),
+
+so every head attends with a query of rank + rot_dim over one shared key row per position whose first `rank` entries
+are also its value: multi-query attention over the pages, between two per-head products."""
+from __future__ import annotations
+
+from .. import ops
+from ..spec import PartSpec, TensorSpec
+from . import linear
+from .base import POSITION_ENCODINGS, CacheRequest, Mixer, make_part, register_mixer, to_f32, to_operand
+
+_NAMES = {"q": "q_proj.weight", "dkv": "kv_down_proj.weight", "c_norm": "kv_norm.weight", "uk": "k_up_proj.weight",
+          "uv": "v_up_proj.weight", "out": "o_proj.weight"}
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_dim: int, kv_rank: int, scale: float, eps: float,
+                 pos: PartSpec, names=None, norm_init: str = "ones"):
+        self.D, self.H, self.dim, self.rd, self.vd, self.rank = hidden_size, num_heads, head_dim, rot_dim, v_dim, kv_rank
+        self.scale, self.eps, self.norm_init = float(scale), float(eps), norm_init
+        if kv_rank > 512:
+            raise ValueError(f"a latent of {kv_rank}: the attention kernels take values up to 512 wide")
+        self.pos = make_part(POSITION_ENCODINGS, "position encoding", pos)
+        if not self.pos.is_identity and (self.pos.rotary_dim > rot_dim or self.pos.pairing != "halves"):
+            raise ValueError("the rotated part turns by halves over at most rot_dim dimensions")
+        self.names = {**_NAMES, **(names or {})}
+
+    def tensors(self):
+        n, H = self.names, self.H
+        init = ("ones",) if self.norm_init == "ones" else ("ones_plus", 0.1)
+        return [TensorSpec(n["q"], (H * (self.dim + self.rd), self.D)), TensorSpec(n["dkv"], (self.rank + self.rd, self.D)),
+                TensorSpec(n["c_norm"], (self.rank,), "f32", init), TensorSpec(n["uk"], (H * self.dim, self.rank)),
+                TensorSpec(n["uv"], (H * self.vd, self.rank)), TensorSpec(n["out"], (self.D, H * self.vd))]
+
+    def bind(self, get, rt):
+        import torch
+        self.rt = rt
+        n, H = self.names, self.H
+        nq = H * (self.dim + self.rd)
+        self.w_qd = torch.empty((nq + self.rank + self.rd, self.D), dtype=rt.dtype, device=rt.device)     # one product: [q | latent | shared key part]
+        self.w_qd[:nq].copy_(get(n["q"]))
+        self.w_qd[nq:].copy_(get(n["dkv"]))
+        self.c_norm = to_f32(get(n["c_norm"]), rt)
+        # per head: a -> W_uk_h^T a is a product with the [rank, dim] matrix W_uk_h^T; o -> W_uv_h o with [vd, rank]
+        self.w_ukT = to_operand(get(n["uk"]), rt).view(H, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = to_operand(get(n["uv"]), rt).view(H, self.vd, self.rank).contiguous()
+        self.w_o = to_operand(get(n["out"]), rt)
+        self.pos.bind(lambda name: get("position." + name), rt)
+
+    def cache_request(self):
+        return CacheRequest("full", None, 1, self.rank + self.rd, v_dim=self.rank, values_in_keys=True)
+
+    def forward(self, xn, ctx, cache, state, out):
+        rt, H = self.rt, self.H
+        T = xn.shape[0]
+        table = ctx.block_tables[cache.group]
+        ops.current_tag = "latent.qkv"
+        x = linear.matmul(xn, self.w_qd, rt)
+        ops.current_tag = "latent.prepare"
+        inv_freq, turn = (None, 0) if self.pos.is_identity else self.pos.rotary_table()[:2]
+        qn, qr = ops.latent_prep(x, H, self.dim, self.rd, self.rank, self.c_norm, self.eps, inv_freq, turn, ctx.positions,
+                                 ctx.req_of_token, table, cache.page_size, cache.k)
+        ops.current_tag = "latent.absorb"
+        ql = linear.batched_matmul(qn.view(H * T, self.dim), self.w_ukT, rt, T)          # FP32 [H T, rank]
+        ops.current_tag = "latent.keys"
+        o = ops.attention_flex(ql, qr.view(H * T, self.rd) if self.rd else None, True, cache.k, cache.v, table, ctx.req_of_token,
+                               ctx.positions, H, self.scale, out_head_major=True)        # [H, T, rank]
+        ops.current_tag = "latent.values"
+        ov = linear.batched_matmul(o.view(H * T, self.rank), self.w_uv, rt, T)           # FP32 [H T, vd]
+        a = ops.heads_to_rows(ov, H, rt.dtype)
+        ops.current_tag = "latent.o"
+        return linear.matmul(a, self.w_o, rt, partials_ok=True)

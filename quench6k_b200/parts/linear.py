@@ -88,3 +88,28 @@ def grouped_matmul(a: torch.Tensor, plan: GroupPlan, w: torch.Tensor, rt) -> tor
     if plan.tc:
         return ops.gemm_simt(a, w, groups=ops.tile_list(plan.tiles[0], plan.pairs, ops.simt_tile_rows()), rows=plan.pairs)
     return ops.gemm_simt(a, w, groups=plan.tiles, rows=plan.pairs)
+
+
+_uniform = {}
+
+
+def _uniform_groups(groups: int, rows_per_group: int, bm: int, device):
+    """The tile list of `groups` groups of equal size, rows group-major; made once per shape (outside any recording)."""
+    key = (groups, rows_per_group, bm, str(device))
+    if key not in _uniform:
+        if len(_uniform) > 512:
+            _uniform.clear()
+        offsets = (torch.arange(groups + 1, dtype=torch.int32) * rows_per_group).to(device)
+        _uniform[key] = ops.tile_list(offsets, groups * rows_per_group, bm)
+    return _uniform[key]
+
+
+def batched_matmul(a: torch.Tensor, w: torch.Tensor, rt, rows_per_group: int) -> torch.Tensor:
+    """FP32 y[g M + r] = a[g M + r] @ w[g]^T for G groups of M = rows_per_group rows each: one product per head, the rows
+    laid out head by head.  a: [G M, K], w: [G, N, K]."""
+    G = w.shape[0]
+    total = G * rows_per_group
+    if _tc(a, w, rt) and a.is_contiguous():
+        bt = ops.tc_token_tile(rows_per_group, False)
+        return ops.gemm_tc(a, w, groups=_uniform_groups(G, rows_per_group, bt, a.device), bt=bt, rows=total)
+    return ops.gemm_simt(a, w, groups=_uniform_groups(G, rows_per_group, ops.simt_tile_rows(), a.device), rows=total)

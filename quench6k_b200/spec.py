@@ -22,9 +22,10 @@ class LayerSpec:
     """One set of layer weights: the parts and how they are arranged in a block."""
     prefix: str                 # tensor-name prefix, e.g. "model.layers.3."
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]     # None: the block has no feed-forward (arrangements that allow it)
     norm: PartSpec              # the kind of both norms of the block
     block: str = "prenorm"      # arrangement, a key of parts.BLOCKS
+    post_norm: Optional[PartSpec] = None    # the kind of the norms on the sublayers' results, in arrangements that have them
 
 
 @dataclass
@@ -41,6 +42,12 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     init_std: float = 0.02                 # std of the random-weights mode for matrices
     name_alias: Optional[Callable[[str], Optional[str]]] = None   # a stored tensor's other name -> the name declared here (or None)
+    # what follows a layer's prefix for each of its parts (a part's own tensor names come after it)
+    sub_names: Dict[str, str] = field(default_factory=lambda: {"norm1": "input_layernorm.", "mixer": "self_attn.",
+                                                                "norm2": "post_attention_layernorm.", "ffn": "mlp."})
+    # executed positions before which the embedding output is added to the stream again (a span of layers run several
+    # times takes its input anew at the start of every pass but the first)
+    readd_embedding: Tuple[int, ...] = ()
 
 
 @dataclass
