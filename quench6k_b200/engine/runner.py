@@ -235,7 +235,7 @@ class ModelRunner:
             total = 3 * T + (R + 1) + 2 * R + n_want + sum(R * w for w in widths)
             static = torch.empty(total, dtype=torch.int32, device=self.rt.device)
             ctx = self._context(entries, widths, static, pad)
-            ctx.max_context = max(widths) * self.page_size          # launch plans must hold for every replay
+            ctx.max_context = max(widths, default=0) * self.page_size          # launch plans must hold for every replay
             logits = self.model.forward(ctx, self.caches, self.states)
             result = logits[:real_rows].clone() if logits is not None else None
             torch.cuda.synchronize()

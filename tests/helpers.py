@@ -65,7 +65,8 @@ def schedule_tail(requests, tail=32):
     n = 0
     for rid, toks in requests.items():
         head = max(1, len(toks) - tail)
-        steps.append({"step": n, "entries": [{"id": rid, "tokens": toks[:head], "want": list(range(head))}], "end": []})
+        steps.append({"step": n, "entries": [{"id": rid, "tokens": toks[:head], "want": list(range(head))}],
+                      "end": [rid] if head == len(toks) else []})
         n += 1
         for i in range(head, len(toks)):
             steps.append({"step": n, "entries": [{"id": rid, "tokens": toks[i:i + 1], "want": [0]}],

@@ -1,0 +1,206 @@
+"""The Pedotar decoder in the engine against the plain implementation (tests/plain_pedotar.py): each mechanism alone
+(models of one layer), whole prompts against token-by-token decoding, portions down to two tokens, mixed batches with
+so few pages and slots that both are used again, long decoding, and greedy generation through the engine's entry point.
+
+Where random weights would hide a fault the score scale of the configuration is raised so that the softmax of every
+(position, head) rests on one or two keys: a key that is wrongly seen or wrongly hidden (one position off at a chunk's
+start, a page's border, the far end of a long context) then moves that position's logits by far more than rounding."""
+import pytest
+import torch
+
+import helpers
+import pedotar_configs as pc
+import pedotar_helpers as ph
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+def _replay_and_compare(folder, cfg, weights, requests, steps, max_tokens, dtype, what, page=None, max_requests=4):
+    outputs, runner = helpers.run_replay(folder, dtype, steps, max_tokens, page_size=page, max_requests=max_requests)
+    got = helpers.collect(requests, steps, outputs)
+    worst = 0.0
+    for rid, toks in requests.items():
+        worst = max(worst, ph.assert_close(got[rid], ph.plain(cfg, weights, toks), dtype, f"{what} {dtype} {rid}"))
+    print(f"{what} {dtype}: worst error {worst:.3e}")
+    return got
+
+
+# ------------------------------------------------------------------------------------------------- kernels alone
+@pytest.mark.parametrize("D", [48, 256, 1000])
+def test_layernorm_kernel_steps(D):
+    from quench6k_b200 import ops
+    g = torch.Generator().manual_seed(D)
+    T = 7
+    h = torch.randn(T, D, generator=g).cuda() * 3 + 1
+    y = torch.randn(3, T, D, generator=g).cuda()
+    extra = torch.randn(T, D, generator=g).cuda()
+    wa, ba, w, b = (torch.randn(D, generator=g).cuda() for _ in range(4))
+    eps = 1e-5
+
+    def ln(x, ww, bb):
+        x = x.double()
+        mu = x.mean(-1, keepdim=True)
+        return (x - mu) / torch.sqrt(((x - mu) ** 2).mean(-1, keepdim=True) + eps) * ww.double() + bb.double()
+
+    want_h = h.double() + ln(y.double().sum(0), wa, ba) + extra.double()
+    want_out = ln(want_h, w, b)
+    hh = h.clone()
+    out = ops.layernorm(hh, w, b, eps, torch.float32, after=(y, wa, ba), extra=extra)
+    assert (hh.double() - want_h).abs().max() < 1e-5 and (out.double() - want_out).abs().max() < 2e-5
+    # each step alone, and rows picked for the last norm
+    hh = h.clone()
+    assert ops.layernorm(hh, None, None, eps, torch.float32, after=(y[0], wa, ba)) is None
+    assert (hh.double() - (h.double() + ln(y[0], wa, ba))).abs().max() < 1e-5
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32).cuda()
+    out = ops.layernorm(h, w, b, eps, torch.bfloat16, rows=rows)
+    assert out.dtype == torch.bfloat16 and (out.double() - ln(h[rows.long()], w, b)).abs().max() < 0.05
+
+
+# ------------------------------------------------------------------------------------------------- one mechanism alone
+ONE = {
+    "scan": pc.scan(40, 6, 3, 2),
+    "scan_wide_state": pc.scan(24, 70, 4, 5),
+    "scan_one_tap": pc.scan(33, 3, 1, 1),
+    "latent": pc.latent(3, 8, 6, 10, 12, 200.0, 2.0),
+    "latent_part_turns": pc.latent(2, 16, 8, 4, 24, 10000.0, 1.0, dims=4),
+    "latent_nothing_turns": pc.latent(2, 8, 0, 8, 16, 10000.0, 1.5),
+    "chunked": pc.chunked(4, 2, 8, 12, 5, 3.0),
+    "chunked_one_kv_head": pc.chunked(3, 1, 16, 4, 7, 2.0),
+    "chunked_wide": pc.chunked(2, 2, 40, 40, 64, 1.0),
+}
+
+
+@pytest.fixture(scope="module", params=sorted(ONE))
+def single(request, tmp_path_factory):
+    name = request.param
+    folder = str(tmp_path_factory.mktemp(name))
+    cfg, weights = ph.make_folder(folder, pc.one_layer(ONE[name]), seed=3, init_std=0.3)
+    reqs = {"long": helpers.random_tokens(330, cfg["vocab"], 1), "short": helpers.random_tokens(9, cfg["vocab"], 2),
+            "one": helpers.random_tokens(1, cfg["vocab"], 3)}
+    return name, folder, cfg, weights, reqs
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mechanism_alone_whole_prompt(single, dtype):
+    name, folder, cfg, weights, reqs = single
+    steps, mt = helpers.schedule_whole(reqs)
+    _replay_and_compare(folder, cfg, weights, reqs, steps, mt, dtype, f"{name} whole")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mechanism_alone_token_by_token(single, dtype):
+    """Every token decoded alone from the first one on: each key is found through the cache, each state through its slot."""
+    name, folder, cfg, weights, reqs = single
+    reqs = {"long": reqs["long"][:150], "short": reqs["short"]}
+    steps, mt = helpers.schedule_tail(reqs, tail=10 ** 6)
+    _replay_and_compare(folder, cfg, weights, reqs, steps, mt, dtype, f"{name} decoded")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mechanism_alone_portions(single, dtype):
+    name, folder, cfg, weights, reqs = single
+    for seed in (0, 1):
+        steps, mt = helpers.schedule_portions(reqs, seed=seed)
+        _replay_and_compare(folder, cfg, weights, reqs, steps, mt, dtype, f"{name} portions")
+
+
+def test_a_hidden_key_would_show(single):
+    """The premise of the tests above: in these models one key more or less in a softmax is far beyond the tolerance.
+    The plain implementation with the chunk (or the causal edge) moved by one position differs from itself."""
+    name, folder, cfg, weights, reqs = single
+    if "chunked" not in name:
+        pytest.skip("the check is written for the chunked mask")
+    other = pc.one_layer(ONE[name])
+    other["layers"][0]["mixer"]["mask"]["size"] += 1
+    a, b = ph.plain(cfg, weights, reqs["long"]), ph.plain(other, weights, reqs["long"])
+    moved = ((a - b).abs().max(-1).values / a.abs().max()) > 3 * ph.TOL["bfloat16"]
+    assert moved.float().mean() > 0.15
+
+
+# ------------------------------------------------------------------------------------------------- whole models
+LENGTHS = {"P1": [71, 130, 45, 96, 64, 33, 1, 58, 77], "P2": [85, 140, 37, 101, 2, 50, 90, 125, 44], "P3": [90, 257, 129, 48, 75, 40, 310, 66, 83]}
+
+
+@pytest.fixture(scope="module", params=["P1", "P2", "P3"])
+def model(request, tmp_path_factory):
+    name = request.param
+    folder = str(tmp_path_factory.mktemp(name))
+    cfg, weights = ph.make_folder(folder, pc.get(name), seed=7)
+    reqs = {f"r{i}": helpers.random_tokens(n, cfg["vocab"], 100 + i) for i, n in enumerate(LENGTHS[name])}
+    return {"name": name, "folder": folder, "cfg": cfg, "weights": weights, "requests": reqs}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_model_whole(model, dtype):
+    steps, mt = helpers.schedule_whole(model["requests"])
+    _replay_and_compare(model["folder"], model["cfg"], model["weights"], model["requests"], steps, mt, dtype, model["name"] + " whole")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_model_prefill_then_decode(model, dtype):
+    steps, mt = helpers.schedule_tail(model["requests"], tail=40)
+    _replay_and_compare(model["folder"], model["cfg"], model["weights"], model["requests"], steps, mt, dtype, model["name"] + " tail")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_model_portions(model, dtype):
+    steps, mt = helpers.schedule_portions(model["requests"], seed=5)
+    _replay_and_compare(model["folder"], model["cfg"], model["weights"], model["requests"], steps, mt, dtype, model["name"] + " portions")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_model_mixed_batches_reuse_pages_and_slots(model, dtype):
+    """Up to four live requests, unequal portions beside single tokens, requests that sit steps out; nine requests go
+    through four slots and a pool of the live requests' size, so every slot and most pages are used again."""
+    page = model["cfg"]["kv_page_size"]
+    for seed in (0, 1):
+        steps, mt = helpers.schedule_mixed(model["requests"], page, seed=seed, max_live=4)
+        got = _replay_and_compare(model["folder"], model["cfg"], model["weights"], model["requests"], steps, mt, dtype,
+                                  model["name"] + " mixed", max_requests=4)
+    # and the same requests each alone: what else is in the batch changes nothing beyond rounding
+    steps, mt = helpers.schedule_whole(model["requests"])
+    outputs, _ = helpers.run_replay(model["folder"], dtype, steps, mt)
+    alone = helpers.collect(model["requests"], steps, outputs)
+    for rid in model["requests"]:
+        ph.assert_close(got[rid], alone[rid], dtype, f"{model['name']} {dtype} {rid} batched against alone", tol=2 * ph.TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_model_many_decoding_together(model, dtype):
+    page = model["cfg"]["kv_page_size"]
+    reqs = {rid: t for rid, t in model["requests"].items() if len(t) > 12}
+    steps, mt = helpers.schedule_wide_decode(reqs, page)
+    _replay_and_compare(model["folder"], model["cfg"], model["weights"], reqs, steps, mt, dtype, model["name"] + " wide decode",
+                        max_requests=len(reqs))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model, dtype):
+    """A short prompt and hundreds of tokens decoded one by one: chunks and pages pass over decoded tokens, the recurrent
+    state runs long, the decode steps are replayed from a recorded graph."""
+    reqs = {"d": helpers.random_tokens(420, model["cfg"]["vocab"], 9)}
+    steps, mt = helpers.schedule_tail(reqs, tail=410)
+    _replay_and_compare(model["folder"], model["cfg"], model["weights"], reqs, steps, mt, dtype, model["name"] + " long decode")
+
+
+def test_greedy_generation_through_the_engine(model):
+    """Engine.generate (scheduler, continuous batching, device-side argmax, CUDA graphs) against greedy decoding with the
+    plain implementation, float32; prompts of unequal length in one engine with few pages."""
+    import quench6k_b200 as q
+    cfg, weights = model["cfg"], model["weights"]
+    prompts = [helpers.random_tokens(n, cfg["vocab"], 50 + n) for n in (5, 23, 1, 40, 12, 31)]
+    page = cfg["kv_page_size"]
+    eng = q.Engine.from_folder(model["folder"], dtype="float32", page_size=page, num_pages=4 * (64 // page + 2), max_requests=4,
+                               max_batch_tokens=32)
+    outs = eng.generate(prompts, q.SamplingParams(max_tokens=12, temperature=0))
+    for prompt, out in zip(prompts, outs):
+        toks = list(prompt)
+        for i in range(12):
+            logits = ph.plain(cfg, weights, toks)[-1]
+            top2 = logits.topk(2).values
+            if float(top2[0] - top2[1]) < 1e-3 * float(logits.abs().max()):
+                break                                  # a near-tie: float32 may pick either; the continuation is not comparable
+            assert out.tokens[i] == int(logits.argmax()), f"{model['name']}: prompt of {len(prompt)}, generated token {i}"
+            toks.append(out.tokens[i])
+    eng.runner.manager.check()
