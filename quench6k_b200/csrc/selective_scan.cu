@@ -94,7 +94,9 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* u, const f
                 for (int k = 0; k < MAX_PER_LANE; ++k) {
                     const int n = sub + L * k;
                     if (n < N) {
-                        S[k] = fmaf(expf(dt * a[k]), S[k], du * Bt[n]);
+                        // exp(dt A) S as S + expm1(dt A) S: a decay close to 1 keeps its distance from 1 to full precision, so
+                        // that no rounding of the factor itself (always the same way for a given dt A) adds up over a long context
+                        S[k] = fmaf(expm1f(dt * a[k]), S[k], S[k]) + du * Bt[n];
                         y = fmaf(S[k], Ct[n], y);
                     }
                 }
