@@ -57,7 +57,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
 
 
 # kernels launched per exported function (for launch accounting in benchmarks)
-_LAUNCHES = {"q6k_moe_permute": 3, "q6k_moe_plan": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
+_LAUNCHES = {"q6k_attention_flex_mma": 2, "q6k_moe_permute": 3, "q6k_moe_plan": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
 launch_count = 0
 
 
@@ -1110,13 +1110,16 @@ def heads_to_rows(src: torch.Tensor, H: int, out_dtype: torch.dtype) -> torch.Te
 def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], head_major: bool, k_pages: torch.Tensor, v_pages: torch.Tensor,
                    block_table: torch.Tensor, req_of_token: torch.Tensor, positions: torch.Tensor, H: int, scale: float,
                    window: Optional[int] = None, chunk: Optional[int] = None, talk: Optional[torch.Tensor] = None,
-                   out_head_major: bool = False) -> torch.Tensor:
+                   out_head_major: bool = False, tiles=None, max_context: int = 0) -> torch.Tensor:
     """Causal attention of every row over its request's pages, for any key and value widths.  A query row is the FP32
     part q_f32 [H*T or T*H rows, da] followed by q [rows, db] in the pages' dtype (either may be None); rows are head-major
     (h T + t) or token-major.  k_pages [Hkv, P, page, dk]; v_pages [Hkv, P, page, dv], possibly a view into k_pages (the
     last axis contiguous, the others with k's strides).  window: only the last `window` keys; chunk: only keys of the
     position's own block of `chunk` positions; talk FP32 [H, H]: the heads' softmax weights are mixed by it before the
-    values.  Returns [H, T, dv] (out_head_major) or [T, H dv]."""
+    values.  Returns [H, T, dv] (out_head_major) or [T, H dv].
+    tiles = (first row, token count, number) of row tiles of attention_flex_tile_tokens(H, Hkv) tokens of one request
+    each, with max_context the largest position + 1 of the step: bfloat16 pages then go to the tensor-core kernel where
+    it takes the shapes (no mixed heads); with few tiles it splits the keys into fixed ranges and merges them."""
     da = q_f32.shape[-1] if q_f32 is not None else 0
     db = q.shape[-1] if q is not None else 0
     rows = (q_f32 if q_f32 is not None else q).numel() // (da if q_f32 is not None else db)
@@ -1135,8 +1138,43 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
     if talk is not None:
         _need(talk, "talk", torch.float32, (H, H))
     out = torch.empty((H, T, dv) if out_head_major else (T, H * dv), dtype=k_pages.dtype, device=k_pages.device)
+    shared_v = v_pages.data_ptr() == k_pages.data_ptr() and v_pages.stride() == k_pages.stride()
+    if (tiles is not None and talk is None and k_pages.dtype == torch.bfloat16
+            and attention_flex_mma_supported(H, Hkv, dk, dv, k_pages.stride(2), v_pages.stride(2), db, shared_v)):
+        tok0, ntok, n_tiles = tiles
+        nsplit, split_keys, ws = 1, 0, None
+        ctas = n_tiles * Hkv
+        if ctas < 120 and not window and not chunk and max_context > 256:       # few row tiles: fixed key ranges over more CTAs
+            want = max(1, 296 // ctas)
+            split_keys = max(256, (-(-max_context // want) + 63) // 64 * 64)
+            nsplit = -(-max_context // split_keys)
+            if nsplit > 1:
+                lib = library()
+                lib.q6k_attention_flex_mma_workspace.restype = ctypes.c_longlong
+                ws = _workspace(lib.q6k_attention_flex_mma_workspace(_i(T), _i(H), _i(dv), _i(nsplit)), k_pages.device, "flex")
+        _call("q6k_attention_flex_mma", _ptr(q_f32), _i(da), _ptr(q), _i(db), _i(1 if head_major else 0), _ptr(k_pages),
+              _ll(k_pages.stride(0)), _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv),
+              _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _ptr(tok0), _ptr(ntok),
+              _i(n_tiles), _i(window or 0), _i(chunk or 0), _f(scale), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv),
+              _i(nsplit), _i(split_keys), _ptr(ws), _stream())
+        return out
     _call("q6k_attention_flex", _ptr(q_f32), _i(da), _ptr(q), _i(db), _i(1 if head_major else 0), _ptr(k_pages), _ll(k_pages.stride(0)),
           _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _i(window or 0), _i(chunk or 0), _f(scale),
           _ptr(talk), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv), _i(dtype_code(k_pages.dtype)), _stream())
     return out
+
+
+@functools.lru_cache(maxsize=None)
+def attention_flex_mma_supported(H: int, Hkv: int, dk: int, dv: int, k_ld: int, v_ld: int, db: int, shared_v: bool) -> bool:
+    lib = library()
+    lib.q6k_attention_flex_mma_supported.restype = ctypes.c_int
+    return bool(lib.q6k_attention_flex_mma_supported(_i(H), _i(Hkv), _i(dk), _i(dv), _i(k_ld), _i(v_ld), _i(db), _i(1 if shared_v else 0)))
+
+
+@functools.lru_cache(maxsize=None)
+def attention_flex_tile_tokens(H: int, Hkv: int) -> int:
+    """Tokens of one request in a row tile of the tensor-core flexible attention kernel."""
+    lib = library()
+    lib.q6k_attention_flex_mma_tile_tokens.restype = ctypes.c_int
+    return lib.q6k_attention_flex_mma_tile_tokens(_i(H), _i(Hkv))

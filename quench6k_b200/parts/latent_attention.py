@@ -70,8 +70,9 @@ class LatentAttention(Mixer):
         ops.current_tag = "latent.absorb"
         ql = linear.batched_matmul(qn.view(H * T, self.dim), self.w_ukT, rt, T)          # FP32 [H T, rank]
         ops.current_tag = "latent.keys"
+        tiles = None if rt.is_fp32 or not rt.tensor_cores else ctx.query_tiles(ops.attention_flex_tile_tokens(H, 1))
         o = ops.attention_flex(ql, qr.view(H * T, self.rd) if self.rd else None, True, cache.k, cache.v, table, ctx.req_of_token,
-                               ctx.positions, H, self.scale, out_head_major=True)        # [H, T, rank]
+                               ctx.positions, H, self.scale, out_head_major=True, tiles=tiles, max_context=ctx.max_context)   # [H, T, rank]
         ops.current_tag = "latent.values"
         ov = linear.batched_matmul(o.view(H * T, self.rank), self.w_uv, rt, T)           # FP32 [H T, vd]
         a = ops.heads_to_rows(ov, H, rt.dtype)

@@ -204,3 +204,44 @@ def test_greedy_generation_through_the_engine(model):
             assert out.tokens[i] == int(logits.argmax()), f"{model['name']}: prompt of {len(prompt)}, generated token {i}"
             toks.append(out.tokens[i])
     eng.runner.manager.check()
+
+
+# ------------------------------------------------------------------------------------------------- the two attention kernels
+@pytest.mark.parametrize("H, Hkv, da, db, dv, shared, window, chunk", [
+    (16, 1, 128, 16, 128, True, None, None),        # a cached latent: values inside the key rows, part of the query in FP32
+    (8, 1, 512, 64, 512, True, None, None),         # the widest rows the kernel takes
+    (6, 2, 0, 32, 24, False, None, 37),             # groups that do not divide a row tile, chunks
+    (4, 4, 0, 64, 64, False, 50, None),             # one head per group, a window
+    (5, 1, 16, 16, 8, False, 90, 64),               # window and chunks together
+])
+def test_tensor_core_flexible_attention_against_the_plain_kernel(H, Hkv, da, db, dv, shared, window, chunk):
+    """bfloat16 pages: the mma kernel (row tiles, with and without key ranges) against the CUDA-core kernel on the same
+    data, for prompt portions that start anywhere beside single tokens deep into a context, pages in shuffled order."""
+    from quench6k_b200 import ops
+    from quench6k_b200.engine.batch import StepContext
+    g = torch.Generator().manual_seed(H * 1000 + da + dv)
+    page, dk = 16, da + db
+    q_lens, starts = [70, 1, 1, 9, 33], [0, 1500, 63, 700, 250]
+    n_pages = sum((s + n + page - 1) // page for s, n in zip(starts, q_lens))
+    order = torch.randperm(n_pages, generator=g).tolist()
+    tables, at = [], 0
+    for s, n in zip(starts, q_lens):
+        k = (s + n + page - 1) // page
+        tables.append(order[at:at + k])
+        at += k
+    ctx = helpers.make_context(q_lens, starts, [tables])
+    T = ctx.T
+    k_pages = (torch.randn(Hkv, n_pages, page, dk, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    v_pages = k_pages[..., :dv] if shared else (torch.randn(Hkv, n_pages, page, dv, generator=g)).to(torch.bfloat16).cuda()
+    qa = torch.randn(H * T, da, generator=g).cuda() if da else None
+    qb = torch.randn(H * T, db, generator=g).to(torch.bfloat16).cuda() if db else None
+    common = dict(window=window, chunk=chunk, out_head_major=True)
+    want = ops.attention_flex(qa, qb, True, k_pages, v_pages, ctx.block_tables[0], ctx.req_of_token, ctx.positions, H, 0.2, **common)
+    tiles = ctx.query_tiles(ops.attention_flex_tile_tokens(H, Hkv))
+    for max_context in (0, max(s + n for s, n in zip(starts, q_lens))):      # 0: one key range; else fixed ranges, merged
+        before = ops.launch_count
+        got = ops.attention_flex(qa, qb, True, k_pages, v_pages, ctx.block_tables[0], ctx.req_of_token, ctx.positions, H, 0.2,
+                                 tiles=tiles, max_context=max_context, **common)
+        assert ops.launch_count - before == 2, "the tensor-core kernel did not take the shape"
+        err = (got.float() - want.float()).abs().max().item() / want.float().abs().max().item()
+        assert err < 2e-2, f"max_context {max_context}: {err:.3e}"
