@@ -7,8 +7,10 @@
 // tokens of one request.  Keys come in tiles of 64 (aligned to multiples of 64 of the key index).  For each tile every
 // warp computes the scores of all 32 rows against 8 of the keys (QK^T over the key width with mma.sync m16n8k16,
 // operands through ldmatrix from shared memory), the row maxima and sums are exchanged through shared memory, the
-// weights go to shared memory as bfloat16, and every warp adds weights x values into its own eighth of the value
-// width (FP32 accumulators in registers: 32 rows x dv / 8 columns).  Scores, maxima, exponentials and sums are FP32.
+// weights go to shared memory as two bfloat16 terms (the rounded weight and what the rounding left, so that together
+// they carry 16 bits of the FP32 weight), and every warp adds weights x values into its own eighth of the value width
+// with one product per term (FP32 accumulators in registers: 32 rows x dv / 8 columns).  Scores, maxima, exponentials
+// and sums are FP32.
 //
 // With few row tiles (decode steps) the keys are also split over blockIdx.z in fixed ranges of `split_keys` keys;
 // each range leaves an unnormalised partial result with its maximum and sum, and a second kernel merges the ranges in
@@ -72,7 +74,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
     __nv_bfloat16* Vs = shared_v ? Ks : Ks + KEYS * ldq;                        // [KEYS][ldv] (or the key tile itself)
     const int ldvs = shared_v ? ldq : ldv;
     __nv_bfloat16* Ps = (shared_v ? Ks + KEYS * ldq : Vs + KEYS * ldv);         // [ROWS][KEYS + PAD]
-    float* wmax = reinterpret_cast<float*>(Ps + ROWS * (KEYS + PAD));           // [WARPS][ROWS]
+    __nv_bfloat16* Pl = Ps + ROWS * (KEYS + PAD);                               // the same shape: what rounding the weights left
+    float* wmax = reinterpret_cast<float*>(Pl + ROWS * (KEYS + PAD));           // [WARPS][ROWS]
     float* wsum = wmax + WARPS * ROWS;                                          // [WARPS][ROWS]
     int* row_pos = reinterpret_cast<int*>(wsum + WARPS * ROWS);                 // [ROWS]
     int* row_lo = row_pos + ROWS;                                               // [ROWS]
@@ -229,8 +232,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
                 sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
                 if ((lane & 3) == 0) wsum[warp * ROWS + r] = sum;
-                __nv_bfloat162 pp = __floats2bfloat162_rn(s[mb][hf * 2], s[mb][hf * 2 + 1]);
+                const __nv_bfloat162 pp = __floats2bfloat162_rn(s[mb][hf * 2], s[mb][hf * 2 + 1]);
                 *reinterpret_cast<__nv_bfloat162*>(Ps + r * (KEYS + PAD) + warp * 8 + qc) = pp;
+                *reinterpret_cast<__nv_bfloat162*>(Pl + r * (KEYS + PAD) + warp * 8 + qc) =
+                    __floats2bfloat162_rn(s[mb][hf * 2] - __low2float(pp), s[mb][hf * 2 + 1] - __high2float(pp));
             }
         }
         __syncthreads();
@@ -254,9 +259,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
         const __nv_bfloat16* pa0 = Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * (KEYS + PAD) + (lane >> 4) * 8;
 #pragma unroll
         for (int k0 = 0; k0 < KEYS; k0 += 16) {
-            unsigned p0[4], p1[4];
+            unsigned p0[4], p1[4], r0[4], r1[4];
             ldmatrix_x4(p0[0], p0[1], p0[2], p0[3], pa0 + k0);
             ldmatrix_x4(p1[0], p1[1], p1[2], p1[3], pa0 + 16 * (KEYS + PAD) + k0);
+            ldmatrix_x4(r0[0], r0[1], r0[2], r0[3], pa0 + ROWS * (KEYS + PAD) + k0);
+            ldmatrix_x4(r1[0], r1[1], r1[2], r1[3], pa0 + (ROWS + 16) * (KEYS + PAD) + k0);
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
                 const int blk = warp * NB + nb;
@@ -265,6 +272,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
                     ldmatrix_x2_trans(b0, b1, Vs + (k0 + (lane & 15)) * ldvs + blk * 8);
                     mma_bf16(o[0][nb], p0[0], p0[1], p0[2], p0[3], b0, b1);
                     mma_bf16(o[1][nb], p1[0], p1[1], p1[2], p1[3], b0, b1);
+                    mma_bf16(o[0][nb], r0[0], r0[1], r0[2], r0[3], b0, b1);
+                    mma_bf16(o[1][nb], r1[0], r1[1], r1[2], r1[3], b0, b1);
                 }
             }
         }
@@ -331,7 +340,7 @@ __global__ void __launch_bounds__(128) attention_flex_merge_kernel(const float* 
 size_t flex_mma_smem(int dk, int dv, bool shared_v) {
     size_t b = (size_t)(ROWS + KEYS) * (dk + PAD) * 2;
     if (!shared_v) b += (size_t)KEYS * (dv + PAD) * 2;
-    b += (size_t)ROWS * (KEYS + PAD) * 2 + (size_t)2 * WARPS * ROWS * 4 + (size_t)(2 * ROWS + KEYS) * 4;
+    b += (size_t)2 * ROWS * (KEYS + PAD) * 2 + (size_t)2 * WARPS * ROWS * 4 + (size_t)(2 * ROWS + KEYS) * 4;
     return b;
 }
 
