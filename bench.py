@@ -257,6 +257,98 @@ def profile_ops(args, runner, cfg_d, layers, ctx, stand_at_context, rand_ids):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- another design beside Flint
+def pedotar_config(size):
+    """Pedotar at layer sizes that resemble a real model's: per pass a selective scan, attention over a cached latent, chunked
+    attention with mixed heads and another scan, the attention layers with a dense feed-forward; the span runs twice."""
+    D, ff, inner, rank, heads, kv, chunk = {"s": (1024, 4096, 2048, 256, 8, 2, 512), "m": (2048, 8192, 4096, 512, 16, 4, 1024)}[size]
+    scan = {"type": "mamba1", "mixer": {"inner": inner, "state": 16, "conv": 4, "dt_rank": D // 16}, "mlp": None}
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+              "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": rank, "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}}
+    chunked = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+               "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": chunk}}}
+    return {"architecture": "Pedotar", "vocab": 32768, "width": D, "norm": {"eps": 1e-6}, "kv_page_size": 16,
+            "layers": [scan, latent, chunked, dict(scan)], "loop": {"start": 0, "stop": 4, "times": 2}}
+
+
+def flint_dense_config(size):
+    """The closest existing model at equal size: Flint with dense feed-forwards only, the same width, heads, feed-forward
+    width, vocabulary and number of executed layers."""
+    D, ff, _, _, heads, kv, _ = {"s": (1024, 4096, 0, 0, 8, 2, 0), "m": (2048, 8192, 0, 0, 16, 4, 0)}[size]
+    return {"architectures": ["FlintForCausalLM"], "hidden_size": D, "num_hidden_layers": 8, "num_attention_heads": heads,
+            "num_key_value_heads": kv, "head_dim": 128, "vocab_size": 32768, "n_routed_experts": 8, "num_experts_per_tok": 2,
+            "moe_intermediate_size": 64, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "first_k_dense_replace": 8,
+            "intermediate_size": ff, "kv_page_size": 16}
+
+
+def design_compare(args):
+    """Prefill and decode throughput of the Pedotar design beside Flint with dense feed-forwards at equal layer sizes (random
+    weights), and where each model's eager steps spend their time, launcher by launcher.  One JSON line."""
+    import torch
+    from quench6k_b200 import ops
+    from quench6k_b200.config.registry import get_architecture
+    from quench6k_b200.engine import ModelRunner, StepEntry
+    pk = peaks()
+    B, ctx, T, page = args.batch or 8, args.context or 4096, args.prefill_tokens, 16
+    gen = torch.Generator().manual_seed(1)
+    out = {"design": args.design, "dtype": args.dtype, "batch": B, "context": ctx, "prefill_tokens": T, "steps": args.steps,
+           "warmup": args.warmup, "peaks": pk["source"], "sizes": {}}
+    for size in [x for x in args.sizes.split(",") if x]:
+        row = {}
+        for name, cfg_d in (("pedotar", pedotar_config(size)), ("flint_dense", flint_dense_config(size))):
+            arch = get_architecture(cfg_d.get("architecture") or cfg_d["architectures"][0])
+            cfg = arch.config_cls.from_dict(cfg_d)
+            pages = B * ((ctx + args.steps + args.warmup + 64) // page + 2) + T // page + 2
+            runner = ModelRunner.from_random(cfg, 0, dtype=args.dtype, page_size=page, num_pages=pages, max_requests=B + 1, arch=arch)
+            V = runner.vocab_size
+            ids = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
+
+            def timed(fn, n, warm):
+                for i in range(warm):
+                    fn(i)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(warm, warm + n):
+                    fn(i)
+                e1.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1) / n
+
+            # prefill: one prompt of T tokens in one step, a new request every time
+            def prefill(i):
+                runner.add_request(("p", i))
+                runner.step([StepEntry(("p", i), ids(T), [T - 1])])
+                runner.end_request(("p", i))
+            ms_p = timed(prefill, max(3, args.steps // 4), 3)
+            ops.profile_begin()
+            prefill(10 ** 6)
+            prof_p = ops.profile_end()
+            # decode: B requests brought to the context by real prefill steps (the recurrent states are then real too)
+            rids = [("d", j) for j in range(B)]
+            for r in rids:
+                runner.add_request(r)
+                for at in range(0, ctx, T):
+                    runner.step([StepEntry(r, ids(min(T, ctx - at)), [])])
+            toks = [ids(args.steps + args.warmup + 8) for _ in rids]
+            ms_d = timed(lambda i: runner.step([StepEntry(r, [toks[j][i]], [0]) for j, r in enumerate(rids)]), args.steps, args.warmup)
+            runner.cuda_graphs = False
+            ops.profile_begin()
+            runner.step([StepEntry(r, [toks[j][-1]], [0]) for j, r in enumerate(rids)])
+            prof_d = ops.profile_end()
+            assert ops.tc_status() == 0
+            table = lambda rec: sorted(({"op": tag, "launcher": fn, "calls": calls, "us": round(ms * 1e3, 1)} for (tag, fn), (calls, ms) in rec.items()),
+                                       key=lambda x: -x["us"])
+            row[name] = {"prefill_tok_s": round(T / ms_p * 1e3), "prefill_ms": round(ms_p, 3), "decode_tok_s": round(B / ms_d * 1e3),
+                         "decode_ms": round(ms_d, 3), "graph_replays": runner.graph_replays,
+                         "prefill_kernels": table(prof_p), "decode_kernels": table(prof_d)}
+            del runner
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+    print(json.dumps(out))
+    return 0
+
+
 def workload_stress(args, shape):
     """A long prompt beside many short sampled requests, through the engine's own scheduler and
     paged cache: one request of `--context` (131,072) uniform-random tokens, greedy, 128 new tokens;
@@ -348,6 +440,10 @@ def main():
     ap.add_argument("--profile-ops", action="store_true",
                     help="instead of the benchmark line: where an eager decode step and a prefill step spend their time, launcher by "
                          "launcher (CUDA events around every launch; its own JSON line)")
+    ap.add_argument("--design", default=None, choices=["pedotar"],
+                    help="instead of the benchmark line: prefill and decode throughput of that design beside Flint with dense feed-forwards "
+                         "at equal layer sizes (--sizes), with each model's time launcher by launcher (its own JSON line)")
+    ap.add_argument("--sizes", default="s,m", help="--design: s (width 1024) and/or m (width 2048)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill"],
                     help="time one kernel alone at the configuration's head sizes instead of the model: attention_prefill runs "
                          "--prefill-tokens query tokens that end at position --context (one request, contiguous pages)")
@@ -371,6 +467,9 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     if args.kernel == "attention_prefill":
         return kernel_attention_prefill(args)
+    if args.design:
+        torch.cuda.set_device(0)
+        return design_compare(args)
     torch.cuda.set_device(0)
     pk = peaks()
     shape = SHAPES[args.config]

@@ -1,7 +1,7 @@
 // The flexible attention of attention_flex.cu on tensor cores, for bfloat16 storage: any key width that is a multiple
 // of 16 and any value width that is a multiple of 8 up to 512, values optionally a leading slice of the key rows, a
-// query given as an FP32 part and a bfloat16 part, causal mask narrowed by a window and/or chunks.  (The variant that
-// mixes the heads' weights stays on the CUDA-core kernel.)
+// query given as an FP32 part and a bfloat16 part, causal mask narrowed by a window and/or chunks, and the heads'
+// softmax weights mixed by a matrix (see the end of this comment).
 //
 // A CTA of 8 warps takes 32 query rows that share their keys: the G query heads of one KV head for 32 / G consecutive
 // tokens of one request.  Keys come in tiles of 64 (aligned to multiples of 64 of the key index).  For each tile every
@@ -15,6 +15,11 @@
 // With few row tiles (decode steps) the keys are also split over blockIdx.z in fixed ranges of `split_keys` keys;
 // each range leaves an unnormalised partial result with its maximum and sum, and a second kernel merges the ranges in
 // order.  The ranges depend on the key index only, so a position's sums do not depend on the batch around it.
+//
+// Mixed heads: out_h = sum_g talk[h, g] * (softmax_g x V of h's KV head), so every head's weights are needed against the
+// values of every KV head.  blockIdx.z then names the value head: the CTA of (row tile, key head, value head) leaves
+// softmax_g x V_value-head for its G query heads as FP32, and a second kernel takes the sum over g with the FP32 mixing
+// matrix.  The scores are computed once per value head; with chunks the keys a row sees are few.
 #include "common.cuh"
 
 namespace {
@@ -35,6 +40,7 @@ struct MmaArgs {
     float* part_o; float* part_ml;      // [splits][rows][dv], [splits][rows][2] when the keys are split
     int split_keys, nsplit;
     int T_, H, Hkv;
+    int v_heads;                        // > 0 (mixed heads): blockIdx.z is the value head and part_o is [T, H, v_heads, dv]
 };
 
 __device__ __forceinline__ int first_visible_mma(int pos, int window, int chunk) {
@@ -81,7 +87,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
     int* row_lo = row_pos + ROWS;                                               // [ROWS]
     int* key_row = row_lo + ROWS;                                               // [KEYS]
 
-    const int tile = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
+    const int tile = blockIdx.x, kh = blockIdx.y, split = a.v_heads > 0 ? 0 : blockIdx.z, vh = a.v_heads > 0 ? blockIdx.z : kh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tok0 = a.tile_tok0[tile], ntok = a.tile_ntok[tile];
     const int* bt = a.block_table + (size_t)a.req_of_token[tok0] * a.max_blocks;
@@ -138,7 +144,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
     }
     const int total_nb = (a.dv + 7) / 8;
     const __nv_bfloat16* kp = a.k_pages + (size_t)kh * a.k_head_stride;
-    const __nv_bfloat16* vp = a.v_pages + (size_t)kh * a.v_head_stride;
+    const __nv_bfloat16* vp = a.v_pages + (size_t)vh * a.v_head_stride;
 
     for (int j0 = k_begin & ~(KEYS - 1); j0 < k_end; j0 += KEYS) {
         __syncthreads();                                                         // the tile before is no longer read
@@ -287,7 +293,15 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
             const int tk = r / G, g = r % G;
             if (tk >= ntok || tk >= tokens) continue;
             const int t = tok0 + tk, h = kh * G + g;
-            if (a.nsplit > 1) {
+            if (a.v_heads > 0) {
+                const float inv = l_run[mb][hf] > 0.0f ? 1.0f / l_run[mb][hf] : 0.0f;
+                float* dst = a.part_o + (((size_t)t * a.H + h) * a.v_heads + vh) * a.dv;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    const int d = (warp * NB + nb) * 8 + qc;
+                    if (d < a.dv) *reinterpret_cast<float2*>(dst + d) = make_float2(o[mb][nb][hf * 2] * inv, o[mb][nb][hf * 2 + 1] * inv);
+                }
+            } else if (a.nsplit > 1) {
                 const size_t prow = ((size_t)split * a.T_ + t) * a.H + h;
                 if (warp == 0 && (lane & 3) == 0) {
                     a.part_ml[prow * 2] = m_run[mb][hf];
@@ -337,6 +351,18 @@ __global__ void __launch_bounds__(128) attention_flex_merge_kernel(const float* 
     }
 }
 
+// out[t, h] = sum_g talk[h, g] * part[t, g, KV head of h], FP32 sums in the order of g.
+__global__ void __launch_bounds__(128) attention_talk_mix_kernel(const float* part, const float* talk, int H, int Hkv, int dv,
+                                                                 __nv_bfloat16* out) {
+    pdl_enter();
+    const int t = blockIdx.x, h = blockIdx.y, kv = h / (H / Hkv);
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int g = 0; g < H; ++g) acc = fmaf(talk[h * H + g], part[(((size_t)t * H + g) * Hkv + kv) * dv + d], acc);
+        out[((size_t)t * H + h) * dv + d] = __float2bfloat16_rn(acc);
+    }
+}
+
 size_t flex_mma_smem(int dk, int dv, bool shared_v) {
     size_t b = (size_t)(ROWS + KEYS) * (dk + PAD) * 2;
     if (!shared_v) b += (size_t)KEYS * (dv + PAD) * 2;
@@ -361,12 +387,15 @@ Q6K_API long long q6k_attention_flex_mma_workspace(int T_, int H, int dv, int ns
     return nsplit > 1 ? (long long)nsplit * T_ * H * (dv + 2) * 4 : 0;
 }
 
+// The same with mixed heads: every head's result against every KV head's values.
+Q6K_API long long q6k_attention_flex_mma_talk_workspace(int T_, int H, int Hkv, int dv) { return (long long)T_ * H * Hkv * dv * 4; }
+
 Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int db, int q_head_major, const void* k_pages,
                                    long long k_head_stride, int k_ld, const void* v_pages, long long v_head_stride, int v_ld, int dv,
                                    const int* block_table, int max_blocks, int page_size, const int* req_of_token, const int* positions,
                                    const int* tile_tok0, const int* tile_ntok, int n_tiles, int window, int chunk, float scale, void* out,
                                    int out_head_major, int T_, int H, int Hkv, int nsplit, int split_keys, float* workspace,
-                                   cudaStream_t st) {
+                                   const float* talk, cudaStream_t st) {
     if (T_ == 0 || n_tiles == 0) return 0;
     const int dk = da + db;
     const bool shared_v = v_pages == k_pages && v_ld == k_ld && v_head_stride == k_head_stride;
@@ -374,13 +403,15 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
     Q6K_REQUIRE((da == 0 || qa) && (db == 0 || qb) && nsplit >= 1 && (nsplit == 1 || (workspace && split_keys > 0 && split_keys % KEYS == 0)),
                 "attention_flex_mma: bad query parts or key split");
     Q6K_REQUIRE(Hkv <= 65535 && nsplit <= 65535, "attention_flex_mma: grid too large");
+    Q6K_REQUIRE(!talk || (nsplit == 1 && workspace && !out_head_major), "attention_flex_mma: mixed heads take one key range, scratch and token-major output");
     MmaArgs a{qa, da, (const __nv_bfloat16*)qb, db, q_head_major, (const __nv_bfloat16*)k_pages, k_head_stride, k_ld,
               (const __nv_bfloat16*)v_pages, v_head_stride, v_ld, dv, block_table, max_blocks, page_size, req_of_token, positions,
               tile_tok0, tile_ntok, window, chunk, scale, (__nv_bfloat16*)out, out_head_major,
-              workspace, workspace ? workspace + (size_t)nsplit * T_ * H * dv : nullptr, split_keys, nsplit, T_, H, Hkv};
+              workspace, workspace ? workspace + (size_t)nsplit * T_ * H * dv : nullptr, split_keys, nsplit, T_, H, Hkv,
+              talk ? Hkv : 0};
     const size_t smem = flex_mma_smem(dk, dv, shared_v);
     const int nb = ((dv + 7) / 8 + WARPS - 1) / WARPS;
-    dim3 grid(n_tiles, Hkv, nsplit);
+    dim3 grid(n_tiles, Hkv, talk ? Hkv : nsplit);
 #define FLEX_LAUNCH(NB)                                                                                                   \
     do {                                                                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_flex_mma_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -392,6 +423,10 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
     else FLEX_LAUNCH(8);
 #undef FLEX_LAUNCH
     if (int rc = q6k_check_launch("attention_flex_mma")) return rc;
+    if (talk) {
+        q6k_launch(attention_talk_mix_kernel, dim3(T_, H), 128, 0, st, (const float*)workspace, talk, H, Hkv, dv, (__nv_bfloat16*)out);
+        return q6k_check_launch("attention_talk_mix");
+    }
     if (nsplit > 1) {
         q6k_launch(attention_flex_merge_kernel, dim3(T_, H), 128, 0, st, (const float*)a.part_o, (const float*)a.part_ml, nsplit, T_, H, dv,
                    (__nv_bfloat16*)out, out_head_major);

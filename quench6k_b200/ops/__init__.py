@@ -57,7 +57,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
 
 
 # kernels launched per exported function (for launch accounting in benchmarks)
-_LAUNCHES = {"q6k_attention_flex_mma": 2, "q6k_moe_permute": 3, "q6k_moe_plan": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
+_LAUNCHES = {"q6k_attention_flex_mma": 2, "q6k_selective_scan": 1, "q6k_moe_permute": 3, "q6k_moe_plan": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
 launch_count = 0
 
 
@@ -1022,12 +1022,14 @@ def cast_columns(src: torch.Tensor, col0: int, n: int, out_dtype: torch.dtype) -
 
 def selective_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, proj: torch.Tensor, b_col: int, c_col: int,
                    A: torch.Tensor, D: torch.Tensor, xz: torch.Tensor, z_col: int, state: torch.Tensor, tail: torch.Tensor,
-                   q_start: torch.Tensor, slot_ids: torch.Tensor, R: int) -> torch.Tensor:
+                   q_start: torch.Tensor, slot_ids: torch.Tensor, R: int, segments=None) -> torch.Tensor:
     """The selective-scan recurrence over each request's tokens in order, from and into the request's state slot:
     dt = softplus(dt_raw + dt_bias); S <- exp(dt A) S + dt u B; y = (S . C + D u) * silu(z).  u [T, C] (operand dtype),
     dt_raw FP32 [T, C], proj FP32 [T, *] holding B and C (N columns each from b_col, c_col), A FP32 [C, N], xz FP32 [T, *]
     holding the convolution's inputs (columns 0..) and z (columns z_col..), state FP32 [slots, C, N], tail FP32
-    [slots, taps-1, C] (moved on to the portion's end).  Returns [T, C] in u's dtype."""
+    [slots, taps-1, C] (moved on to the portion's end).  Returns [T, C] in u's dtype.
+    segments = (most segments of any request, seg_base int32 [R] on the device, segments in all) from
+    selective_scan_segments(q_lens): long portions are then walked by several blocks each (two launches)."""
     _need(u, "u")
     T, C = u.shape
     N = A.shape[1]
@@ -1043,10 +1045,32 @@ def selective_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor,
     if tuple(state.shape[1:]) != (C, N) or tail.shape[2] != C or tail.shape[0] != state.shape[0]:
         raise KernelError("selective_scan: state shapes disagree")
     out = torch.empty((T, C), dtype=u.dtype, device=u.device)
+    most, seg_base, slots, ws = 1, None, 0, None
+    if segments is not None and segments[0] > 1:
+        most, seg_base, slots = segments
+        lib = library()
+        lib.q6k_selective_scan_workspace.restype = ctypes.c_longlong
+        ws = _workspace(4 * lib.q6k_selective_scan_workspace(_i(slots), _i(R), _i(C), _i(N)), u.device, "scan")
     _call("q6k_selective_scan", _ptr(u), _ptr(dt_raw), _ptr(dt_bias), _ptr(proj), _i(proj.stride(0)), _i(b_col), _i(c_col), _ptr(A), _ptr(D),
           _ptr(xz), _i(xz.stride(0)), _i(z_col), _ptr(state), _ptr(tail), _ptr(q_start), _ptr(slot_ids), _ptr(out), _i(R), _i(C), _i(N),
-          _i(taps), _i(dtype_code(u.dtype)), _stream())
+          _i(taps), _i(dtype_code(u.dtype)), _i(most), _ptr(seg_base), _i(slots), _ptr(ws), _stream())
     return out
+
+
+def selective_scan_segments(q_lens, device):
+    """(most segments of any request, first segment slot of each request as int32 on the device, segments in all) for a
+    step whose requests bring q_lens tokens; (1, None, 0) when no request has more than one segment."""
+    lib = library()
+    lib.q6k_selective_scan_segment.restype = ctypes.c_int
+    seg = lib.q6k_selective_scan_segment()
+    counts = [-(-n // seg) for n in q_lens]
+    if max(counts, default=0) <= 1:
+        return 1, None, 0
+    base, at = [], 0
+    for n in counts:
+        base.append(at)
+        at += n
+    return max(counts), torch.tensor(base, dtype=torch.int32).to(device, non_blocking=True), at
 
 
 def qkv_pages(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, vd: int, q_norm, k_norm, eps: float, rotary, positions: torch.Tensor,
@@ -1119,7 +1143,7 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
     values.  Returns [H, T, dv] (out_head_major) or [T, H dv].
     tiles = (first row, token count, number) of row tiles of attention_flex_tile_tokens(H, Hkv) tokens of one request
     each, with max_context the largest position + 1 of the step: bfloat16 pages then go to the tensor-core kernel where
-    it takes the shapes (no mixed heads); with few tiles it splits the keys into fixed ranges and merges them."""
+    it takes the shapes; with few tiles it splits the keys into fixed ranges and merges them."""
     da = q_f32.shape[-1] if q_f32 is not None else 0
     db = q.shape[-1] if q is not None else 0
     rows = (q_f32 if q_f32 is not None else q).numel() // (da if q_f32 is not None else db)
@@ -1139,12 +1163,16 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
         _need(talk, "talk", torch.float32, (H, H))
     out = torch.empty((H, T, dv) if out_head_major else (T, H * dv), dtype=k_pages.dtype, device=k_pages.device)
     shared_v = v_pages.data_ptr() == k_pages.data_ptr() and v_pages.stride() == k_pages.stride()
-    if (tiles is not None and talk is None and k_pages.dtype == torch.bfloat16
+    if (tiles is not None and k_pages.dtype == torch.bfloat16 and not (talk is not None and out_head_major)
             and attention_flex_mma_supported(H, Hkv, dk, dv, k_pages.stride(2), v_pages.stride(2), db, shared_v)):
         tok0, ntok, n_tiles = tiles
         nsplit, split_keys, ws = 1, 0, None
         ctas = n_tiles * Hkv
-        if ctas < 120 and not window and not chunk and max_context > 256:       # few row tiles: fixed key ranges over more CTAs
+        if talk is not None:                     # every head's weights against every KV head's values, then the mixture
+            lib = library()
+            lib.q6k_attention_flex_mma_talk_workspace.restype = ctypes.c_longlong
+            ws = _workspace(lib.q6k_attention_flex_mma_talk_workspace(_i(T), _i(H), _i(Hkv), _i(dv)), k_pages.device, "flex")
+        elif ctas < 120 and not window and not chunk and max_context > 256:     # few row tiles: fixed key ranges over more CTAs
             want = max(1, 296 // ctas)
             split_keys = max(256, (-(-max_context // want) + 63) // 64 * 64)
             nsplit = -(-max_context // split_keys)
@@ -1156,7 +1184,7 @@ def attention_flex(q_f32: Optional[torch.Tensor], q: Optional[torch.Tensor], hea
               _ll(k_pages.stride(0)), _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv),
               _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _ptr(tok0), _ptr(ntok),
               _i(n_tiles), _i(window or 0), _i(chunk or 0), _f(scale), _ptr(out), _i(1 if out_head_major else 0), _i(T), _i(H), _i(Hkv),
-              _i(nsplit), _i(split_keys), _ptr(ws), _stream())
+              _i(nsplit), _i(split_keys), _ptr(ws), _ptr(talk), _stream())
         return out
     _call("q6k_attention_flex", _ptr(q_f32), _i(da), _ptr(q), _i(db), _i(1 if head_major else 0), _ptr(k_pages), _ll(k_pages.stride(0)),
           _i(k_pages.stride(2)), _ptr(v_pages), _ll(v_pages.stride(0)), _i(v_pages.stride(2)), _i(dv), _ptr(block_table),

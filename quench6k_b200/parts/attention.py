@@ -99,8 +99,7 @@ class Attention(Mixer):
                           ctx.positions, ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
                           cache.v if write else None, rt.dtype)
         ops.current_tag = "attention.keys"
-        tiles = (None if rt.is_fp32 or not rt.tensor_cores or self.talk
-                 else ctx.query_tiles(ops.attention_flex_tile_tokens(self.Hq, self.Hkv)))
+        tiles = None if rt.is_fp32 or not rt.tensor_cores else ctx.query_tiles(ops.attention_flex_tile_tokens(self.Hq, self.Hkv))
         a = ops.attention_flex(None, q.view(-1, self.hd), False, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.Hq,
                                self.scale, window=self.window, chunk=self.chunk, talk=self.w_talk, tiles=tiles, max_context=ctx.max_context)
         ops.current_tag = "attention.o"

@@ -61,7 +61,10 @@ class SelectiveScan(Mixer):
         ops.current_tag = "scan.dt"
         dt_raw = linear.matmul(ops.cast_columns(proj, 0, R, rt.dtype), self.w_dt, rt)     # FP32 [T, inner]; bias and softplus in the scan
         ops.current_tag = "scan.recurrence"
+        key = ("scan_segments",)
+        if key not in ctx.plans:                # long portions are walked in segments by several blocks: the same plan for every layer
+            ctx.plans[key] = ops.selective_scan_segments(ctx.q_lens, rt.device)
         y = ops.selective_scan(u, dt_raw, self.dt_b, proj, R, R + N, self.A, self.skip, xz, C, state["ssm"], state["conv"],
-                               ctx.q_start, ctx.slot_ids, ctx.R)
+                               ctx.q_start, ctx.slot_ids, ctx.R, segments=ctx.plans[key])
         ops.current_tag = "scan.out"
         return linear.matmul(y, self.w_o, rt, partials_ok=True)

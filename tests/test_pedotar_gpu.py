@@ -209,6 +209,33 @@ def test_greedy_generation_through_the_engine(model):
 
 
 # ------------------------------------------------------------------------------------------------- the two attention kernels
+@pytest.mark.parametrize("H, Hkv, dk, dv, chunk", [(8, 2, 64, 64, 100), (16, 4, 128, 128, 512), (6, 6, 32, 16, 37), (4, 1, 16, 8, 2000)])
+def test_tensor_core_mixed_heads_against_the_plain_kernel(H, Hkv, dk, dv, chunk):
+    from quench6k_b200 import ops
+    g = torch.Generator().manual_seed(H + dk)
+    page = 16
+    q_lens, starts = [90, 1, 40, 1], [0, 1234, 500, 99]
+    n_pages = sum((s + n + page - 1) // page for s, n in zip(starts, q_lens))
+    order = torch.randperm(n_pages, generator=g).tolist()
+    tables, at = [], 0
+    for s, n in zip(starts, q_lens):
+        k = (s + n + page - 1) // page
+        tables.append(order[at:at + k])
+        at += k
+    ctx = helpers.make_context(q_lens, starts, [tables])
+    k_pages = (torch.randn(Hkv, n_pages, page, dk, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    v_pages = torch.randn(Hkv, n_pages, page, dv, generator=g).to(torch.bfloat16).cuda()
+    q = torch.randn(ctx.T * H, dk, generator=g).to(torch.bfloat16).cuda()
+    talk = torch.randn(H, H, generator=g).cuda()
+    args = (None, q, False, k_pages, v_pages, ctx.block_tables[0], ctx.req_of_token, ctx.positions, H, 0.3)
+    want = ops.attention_flex(*args, chunk=chunk, talk=talk)
+    before = ops.launch_count
+    got = ops.attention_flex(*args, chunk=chunk, talk=talk, tiles=ctx.query_tiles(ops.attention_flex_tile_tokens(H, Hkv)), max_context=2000)
+    assert ops.launch_count - before == 2, "the tensor-core kernel did not take the shape"
+    err = (got.float() - want.float()).abs().max().item() / want.float().abs().max().item()
+    assert err < 2e-2, f"{err:.3e}"
+
+
 @pytest.mark.parametrize("H, Hkv, da, db, dv, shared, window, chunk", [
     (16, 1, 128, 16, 128, True, None, None),        # a cached latent: values inside the key rows, part of the query in FP32
     (8, 1, 512, 64, 512, True, None, None),         # the widest rows the kernel takes
