@@ -40,6 +40,7 @@ struct MmaArgs {
     float* part_o; float* part_ml;      // [splits][rows][dv], [splits][rows][2] when the keys are split
     int split_keys, nsplit;
     int T_, H, Hkv;
+    int nbuf;                           // 2: the next key tile is fetched (cp.async) while this one is used; 1: one buffer
     int v_heads;                        // > 0 (mixed heads): blockIdx.z is the value head and part_o is [T, H, v_heads, dv]
 };
 
@@ -67,6 +68,15 @@ __device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, uns
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// 16 bytes global -> shared without passing registers; !valid: zeros (nothing is read).
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // NB: value n-blocks (of 8 columns) per warp: ceil(ceil(dv / 8) / 8), 1..8.
 template <int NB>
 __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const MmaArgs a) {
@@ -76,16 +86,17 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
     const int ldq = dk + PAD, ldv = a.dv + PAD;
     const bool shared_v = a.v_pages == a.k_pages && a.v_ld == a.k_ld && a.v_head_stride == a.k_head_stride;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);             // [ROWS][ldq]
-    __nv_bfloat16* Ks = Qs + ROWS * ldq;                                        // [KEYS][ldq]
-    __nv_bfloat16* Vs = shared_v ? Ks : Ks + KEYS * ldq;                        // [KEYS][ldv] (or the key tile itself)
+    __nv_bfloat16* Kbase = Qs + ROWS * ldq;                                     // [nbuf][KEYS][ldq]
+    __nv_bfloat16* Vbase = shared_v ? Kbase : Kbase + a.nbuf * KEYS * ldq;      // [nbuf][KEYS][ldv] (or the key tiles themselves)
     const int ldvs = shared_v ? ldq : ldv;
-    __nv_bfloat16* Ps = (shared_v ? Ks + KEYS * ldq : Vs + KEYS * ldv);         // [ROWS][KEYS + PAD]
+    const int k_tile = KEYS * ldq, v_tile = shared_v ? k_tile : KEYS * ldv;
+    __nv_bfloat16* Ps = (shared_v ? Kbase + a.nbuf * k_tile : Vbase + a.nbuf * v_tile);   // [ROWS][KEYS + PAD]
     __nv_bfloat16* Pl = Ps + ROWS * (KEYS + PAD);                               // the same shape: what rounding the weights left
     float* wmax = reinterpret_cast<float*>(Pl + ROWS * (KEYS + PAD));           // [WARPS][ROWS]
     float* wsum = wmax + WARPS * ROWS;                                          // [WARPS][ROWS]
     int* row_pos = reinterpret_cast<int*>(wsum + WARPS * ROWS);                 // [ROWS]
     int* row_lo = row_pos + ROWS;                                               // [ROWS]
-    int* key_row = row_lo + ROWS;                                               // [KEYS]
+    int* key_rows = row_lo + ROWS;                                              // [2][KEYS]
 
     const int tile = blockIdx.x, kh = blockIdx.y, split = a.v_heads > 0 ? 0 : blockIdx.z, vh = a.v_heads > 0 ? blockIdx.z : kh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -146,8 +157,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
     const __nv_bfloat16* kp = a.k_pages + (size_t)kh * a.k_head_stride;
     const __nv_bfloat16* vp = a.v_pages + (size_t)vh * a.v_head_stride;
 
-    for (int j0 = k_begin & ~(KEYS - 1); j0 < k_end; j0 += KEYS) {
-        __syncthreads();                                                         // the tile before is no longer read
+    // the page rows of a tile's keys (-1: not a key of this block), then the tile itself on its way into a buffer
+    auto find_rows = [&](int j0, int buf) {
         if (tid < KEYS) {
             const int j = j0 + tid;
             int row = -1;
@@ -155,26 +166,51 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
                 const int page = bt[j / a.page_size];
                 row = page < 0 ? -1 : page * a.page_size + j % a.page_size;
             }
-            key_row[tid] = row;
+            key_rows[buf * KEYS + tid] = row;
         }
-        __syncthreads();
+    };
+    auto fetch = [&](int buf) {
+        const int* rows_of = key_rows + buf * KEYS;
+        __nv_bfloat16* Kd = Kbase + buf * k_tile;
         for (int i = tid; i < KEYS * (dk / 8); i += blockDim.x) {
-            const int kk = i / (dk / 8), c8 = (i % (dk / 8)) * 8;
-            const int row = key_row[kk];
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (row >= 0) v = *reinterpret_cast<const uint4*>(kp + (size_t)row * a.k_ld + c8);
-            *reinterpret_cast<uint4*>(Ks + kk * ldq + c8) = v;
+            const int kk = i / (dk / 8), c8 = (i % (dk / 8)) * 8, row = rows_of[kk];
+            cp_async16(Kd + kk * ldq + c8, kp + (size_t)(row < 0 ? 0 : row) * a.k_ld + c8, row >= 0);
         }
         if (!shared_v) {
+            __nv_bfloat16* Vd = Vbase + buf * v_tile;
             for (int i = tid; i < KEYS * (a.dv / 8); i += blockDim.x) {
-                const int kk = i / (a.dv / 8), c8 = (i % (a.dv / 8)) * 8;
-                const int row = key_row[kk];
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (row >= 0) v = *reinterpret_cast<const uint4*>(vp + (size_t)row * a.v_ld + c8);
-                *reinterpret_cast<uint4*>(Vs + kk * ldv + c8) = v;
+                const int kk = i / (a.dv / 8), c8 = (i % (a.dv / 8)) * 8, row = rows_of[kk];
+                cp_async16(Vd + kk * ldv + c8, vp + (size_t)(row < 0 ? 0 : row) * a.v_ld + c8, row >= 0);
             }
         }
+        cp_async_commit();
+    };
+    const int j_first = k_begin & ~(KEYS - 1);
+    if (j_first < k_end) {
+        find_rows(j_first, 0);
         __syncthreads();
+        fetch(0);
+    }
+    int it = 0;
+    for (int j0 = j_first; j0 < k_end; j0 += KEYS, ++it) {
+        const int buf = a.nbuf == 2 ? (it & 1) : 0;
+        const bool more = j0 + KEYS < k_end;
+        if (a.nbuf == 2) {
+            if (more) find_rows(j0 + KEYS, buf ^ 1);
+            __syncthreads();                                                     // rows known; the other buffer is no longer read
+            if (more) {
+                fetch(buf ^ 1);
+                cp_async_wait<1>();                                              // this tile has landed, the next is on its way
+            } else {
+                cp_async_wait<0>();
+            }
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const __nv_bfloat16* Ks = Kbase + buf * k_tile;
+        const __nv_bfloat16* Vs = Vbase + buf * v_tile;
+        const int* key_row = key_rows + buf * KEYS;
         // scores of the 32 rows against this warp's 8 keys
         float s[2][4];
 #pragma unroll
@@ -283,6 +319,12 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
                 }
             }
         }
+        if (a.nbuf == 1 && more) {
+            __syncthreads();                                                     // the one buffer is no longer read
+            find_rows(j0 + KEYS, 0);
+            __syncthreads();
+            fetch(0);
+        }
     }
     // results
 #pragma unroll
@@ -363,10 +405,10 @@ __global__ void __launch_bounds__(128) attention_talk_mix_kernel(const float* pa
     }
 }
 
-size_t flex_mma_smem(int dk, int dv, bool shared_v) {
-    size_t b = (size_t)(ROWS + KEYS) * (dk + PAD) * 2;
-    if (!shared_v) b += (size_t)KEYS * (dv + PAD) * 2;
-    b += (size_t)2 * ROWS * (KEYS + PAD) * 2 + (size_t)2 * WARPS * ROWS * 4 + (size_t)(2 * ROWS + KEYS) * 4;
+size_t flex_mma_smem(int dk, int dv, bool shared_v, int nbuf) {
+    size_t b = (size_t)(ROWS + nbuf * KEYS) * (dk + PAD) * 2;
+    if (!shared_v) b += (size_t)nbuf * KEYS * (dv + PAD) * 2;
+    b += (size_t)2 * ROWS * (KEYS + PAD) * 2 + (size_t)2 * WARPS * ROWS * 4 + (size_t)(2 * ROWS + 2 * KEYS) * 4;
     return b;
 }
 
@@ -376,7 +418,7 @@ size_t flex_mma_smem(int dk, int dv, bool shared_v) {
 Q6K_API int q6k_attention_flex_mma_supported(int H, int Hkv, int dk, int dv, int k_ld, int v_ld, int db, int shared_v) {
     if (Hkv <= 0 || H % Hkv || H / Hkv > ROWS) return 0;
     if (dk % 16 || dv % 8 || dv > 512 || k_ld % 8 || v_ld % 8 || db % 8) return 0;
-    return flex_mma_smem(dk, dv, shared_v != 0) <= 220 * 1024;
+    return flex_mma_smem(dk, dv, shared_v != 0, 1) <= 220 * 1024;
 }
 
 // Tokens of one request a row tile holds for this group size.
@@ -408,8 +450,8 @@ Q6K_API int q6k_attention_flex_mma(const float* qa, int da, const void* qb, int 
               (const __nv_bfloat16*)v_pages, v_head_stride, v_ld, dv, block_table, max_blocks, page_size, req_of_token, positions,
               tile_tok0, tile_ntok, window, chunk, scale, (__nv_bfloat16*)out, out_head_major,
               workspace, workspace ? workspace + (size_t)nsplit * T_ * H * dv : nullptr, split_keys, nsplit, T_, H, Hkv,
-              talk ? Hkv : 0};
-    const size_t smem = flex_mma_smem(dk, dv, shared_v);
+              flex_mma_smem(dk, dv, shared_v, 2) <= 220 * 1024 ? 2 : 1, talk ? Hkv : 0};
+    const size_t smem = flex_mma_smem(dk, dv, shared_v, a.nbuf);
     const int nb = ((dv + 7) / 8 + WARPS - 1) / WARPS;
     dim3 grid(n_tiles, Hkv, talk ? Hkv : nsplit);
 #define FLEX_LAUNCH(NB)                                                                                                   \

@@ -30,14 +30,15 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v));
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 // exp(x) - 1 for x <= 0 with a relative error near 1e-7: down to -1/4 the Taylor series in x (its truncation is below
 // x^7 / 40320), beyond that expf(x) - 1, where the exponential's rounding is small beside its distance from 1.
+// FAST (bfloat16 operands, whose own rounding is four orders of magnitude above it): the hardware exponential beyond -1/4
+// (a few units in the last place of the exponential) and two terms fewer in the series.
+template <bool FAST>
 __device__ __forceinline__ float decay_minus_one(float x) {
-    float p = fmaf(x, 1.0f / 5040.0f, 1.0f / 720.0f);
-    p = fmaf(x, p, 1.0f / 120.0f);
-    p = fmaf(x, p, 1.0f / 24.0f);
+    float p = FAST ? fmaf(x, 1.0f / 120.0f, 1.0f / 24.0f) : fmaf(x, fmaf(x, fmaf(x, 1.0f / 5040.0f, 1.0f / 720.0f), 1.0f / 120.0f), 1.0f / 24.0f);
     p = fmaf(x, p, 1.0f / 6.0f);
     p = fmaf(x, p, 0.5f);
     p = fmaf(x, p, 1.0f);
-    return x > -0.25f ? x * p : expf(x) - 1.0f;
+    return x > -0.25f ? x * p : (FAST ? __expf(x) : expf(x)) - 1.0f;
 }
 
 // grid (T, ceil(C / 256)); x: FP32 [T, ldx] (first C columns); tail: FP32 [slots, taps-1, C].
@@ -103,6 +104,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* u, const f
                 if (has) S[k] = fmaf(expm1f(pair[CN + n]), S[k], S[k]) + pair[n];
         }
     }
+    if (MODE == 1 && last_segment) return;     // no later segment folds this one (segment 0 has left the state it found)
     const float bias = live ? dt_bias[c] : 0.0f, dskip = live ? Dskip[c] : 0.0f;
     for (int t0 = 0; t0 < n_tok; t0 += SCAN_TILE) {
         const int nt = min(SCAN_TILE, n_tok - t0);
@@ -142,7 +144,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* u, const f
                         // exp(dt A) S as S + expm1(dt A) S: a decay close to 1 keeps its distance from 1 to full precision, so
                         // that no rounding of the factor itself (always the same way for a given dt A) adds up over a long context
                         const float da = dt * a[k];
-                        S[k] = fmaf(decay_minus_one(da), S[k], S[k]) + du * Bt[n];
+                        S[k] = fmaf(decay_minus_one<sizeof(T) == 2>(da), S[k], S[k]) + du * Bt[n];
                         if (MODE == 1) dsum[k] += da;
                         else y = fmaf(S[k], Ct[n], y);
                     }
