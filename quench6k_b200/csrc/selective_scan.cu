@@ -23,7 +23,7 @@
 namespace {
 
 constexpr int MAX_TAPS = 16;
-constexpr int SCAN_TILE = 16;      // tokens whose B and C rows are staged in shared memory at a time
+constexpr int SCAN_TILE = 32;      // tokens whose inputs are staged in shared memory at a time
 constexpr int MAX_PER_LANE = 8;    // states per lane
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(256) conv_silu_kernel(const float* x, int ldx,
     out[(size_t)t * C + c] = from_f32<T>(silu_f(acc));
 }
 
-// grid (R, ceil(C / (128 / L)), segments), 128 threads; dynamic shared memory 2 * SCAN_TILE * N floats.
+// grid (R, ceil(C / (128 / L)), segments), 128 threads; dynamic shared memory SCAN_TILE * (2 N + 4 * 128 / L) floats.
 // ws (MODE 1, 2): per segment slot q = seg_base[r] + segment, [q][2][C][N] (the state built from zero, the sum of dt A),
 // then per request [r][C][N], the state the step found in the request's slot.
 template <typename T, int MODE>
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* u, const f
                                                              const int* slot_ids, T* out, int C, int N, int L, int taps, float* ws,
                                                              const int* seg_base, int seg_len, int seg_slots) {
     pdl_enter();
-    extern __shared__ float bc[];              // [SCAN_TILE][N] of B, then the same of C
+    extern __shared__ float bc[];              // [SCAN_TILE][N] of B, the same of C, then four [SCAN_TILE][channels of the block]
     const int r = blockIdx.x, seg = MODE == 0 ? 0 : blockIdx.z;
     const int per_block = blockDim.x / L;
     const int c = blockIdx.y * per_block + threadIdx.x / L, sub = threadIdx.x % L;
@@ -105,7 +105,13 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* u, const f
         }
     }
     if (MODE == 1 && last_segment) return;     // no later segment folds this one (segment 0 has left the state it found)
-    const float bias = live ? dt_bias[c] : 0.0f, dskip = live ? Dskip[c] : 0.0f;
+    // Per tile of SCAN_TILE tokens the block first makes, once per (token, channel) and with coalesced loads, what the
+    // recurrence needs of them: dt = softplus(dt_raw + bias), dt u, the gate silu(z) and the skip D u; then B and C.
+    float* s_dt = bc + 2 * SCAN_TILE * N;          // [SCAN_TILE][per_block]
+    float* s_du = s_dt + SCAN_TILE * per_block;
+    float* s_gate = s_du + SCAN_TILE * per_block;
+    float* s_skip = s_gate + SCAN_TILE * per_block;
+    const int c0 = blockIdx.y * per_block, cc = threadIdx.x / L;
     for (int t0 = 0; t0 < n_tok; t0 += SCAN_TILE) {
         const int nt = min(SCAN_TILE, n_tok - t0);
         __syncthreads();
@@ -115,44 +121,43 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* u, const f
             bc[i] = pr[b_col + n];
             bc[SCAN_TILE * N + i] = pr[c_col + n];
         }
-        __syncthreads();
-        float dtv[SCAN_TILE], uv[SCAN_TILE], zv[SCAN_TILE];
-#pragma unroll
-        for (int tt = 0; tt < SCAN_TILE; ++tt) {                 // nothing here waits for the recurrence: all loads of the tile go out together
-            const bool has = live && tt < nt;
-            const size_t row = (size_t)(first + t0 + (has ? tt : 0));
-            dtv[tt] = has ? dt_raw[row * C + c] : 0.0f;
-            uv[tt] = has ? to_f32(u[row * C + c]) : 0.0f;
-            zv[tt] = has && MODE != 1 ? xz[row * ldx + z_col + c] : 0.0f;
-        }
-#pragma unroll
-        for (int tt = 0; tt < SCAN_TILE; ++tt) {
-            dtv[tt] = softplus_f(dtv[tt] + bias);
-            if (MODE != 1) zv[tt] = silu_f(zv[tt]);
-        }
-#pragma unroll
-        for (int tt = 0; tt < SCAN_TILE; ++tt) {
-            if (tt < nt) {
-                const float dt = dtv[tt], du = dtv[tt] * uv[tt];
-                const float* Bt = bc + tt * N;
-                const float* Ct = bc + SCAN_TILE * N + tt * N;
-                float y = 0.0f;
-#pragma unroll
-                for (int k = 0; k < MAX_PER_LANE; ++k) {
-                    const int n = sub + L * k;
-                    if (n < N) {
-                        // exp(dt A) S as S + expm1(dt A) S: a decay close to 1 keeps its distance from 1 to full precision, so
-                        // that no rounding of the factor itself (always the same way for a given dt A) adds up over a long context
-                        const float da = dt * a[k];
-                        S[k] = fmaf(decay_minus_one<sizeof(T) == 2>(da), S[k], S[k]) + du * Bt[n];
-                        if (MODE == 1) dsum[k] += da;
-                        else y = fmaf(S[k], Ct[n], y);
-                    }
-                }
+        for (int i = threadIdx.x; i < nt * per_block; i += blockDim.x) {
+            const int tt = i / per_block, ch = c0 + i % per_block;
+            if (ch < C) {
+                const size_t row = (size_t)(first + t0 + tt);
+                const float dt = softplus_f(dt_raw[row * C + ch] + dt_bias[ch]);
+                const float uu = to_f32(u[row * C + ch]);
+                s_dt[i] = dt;
+                s_du[i] = dt * uu;
                 if (MODE != 1) {
-                    for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-                    if (live && sub == 0) out[(size_t)(first + t0 + tt) * C + c] = from_f32<T>(fmaf(dskip, uv[tt], y) * zv[tt]);
+                    s_gate[i] = silu_f(xz[row * ldx + z_col + ch]);
+                    s_skip[i] = Dskip[ch] * uu;
                 }
+            }
+        }
+        __syncthreads();
+#pragma unroll 2
+        for (int tt = 0; tt < nt; ++tt) {
+            const float dt = s_dt[tt * per_block + cc], du = s_du[tt * per_block + cc];
+            const float* Bt = bc + tt * N;
+            const float* Ct = bc + SCAN_TILE * N + tt * N;
+            float y = 0.0f;
+#pragma unroll
+            for (int k = 0; k < MAX_PER_LANE; ++k) {
+                const int n = sub + L * k;
+                if (n < N) {
+                    // exp(dt A) S as S + expm1(dt A) S: a decay close to 1 keeps its distance from 1 to full precision, so
+                    // that no rounding of the factor itself (always the same way for a given dt A) adds up over a long context
+                    const float da = dt * a[k];
+                    S[k] = fmaf(decay_minus_one<sizeof(T) == 2>(da), S[k], S[k]) + du * Bt[n];
+                    if (MODE == 1) dsum[k] += da;
+                    else y = fmaf(S[k], Ct[n], y);
+                }
+            }
+            if (MODE != 1) {
+                for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+                if (live && sub == 0)
+                    out[(size_t)(first + t0 + tt) * C + c] = from_f32<T>((y + s_skip[tt * per_block + cc]) * s_gate[tt * per_block + cc]);
             }
         }
     }
@@ -246,10 +251,11 @@ Q6K_API int q6k_selective_scan(const void* u, const float* dt_raw, const float* 
     const int per_block = 128 / L;
     dim3 grid(R, (C + per_block - 1) / per_block);
     Q6K_REQUIRE(grid.y <= 65535, "selective_scan: %d channels exceed the grid limit", C);
-    const size_t smem = (size_t)2 * SCAN_TILE * N * sizeof(float);
+    const size_t smem = (size_t)SCAN_TILE * (2 * N + 4 * per_block) * sizeof(float);
     const int seg_len = q6k_selective_scan_segment();
 #define SCAN_LAUNCH(MODE, GRID)                                                                                                      \
-    Q6K_DISPATCH(dtype, q6k_launch(selective_scan_kernel<T, MODE>, GRID, 128, smem, st, (const T*)u, dt_raw, dt_bias, proj, ldp, b_col, c_col, A, \
+    Q6K_DISPATCH(dtype, if (smem > 48 * 1024) cudaFuncSetAttribute(selective_scan_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+                 q6k_launch(selective_scan_kernel<T, MODE>, GRID, 128, smem, st, (const T*)u, dt_raw, dt_bias, proj, ldp, b_col, c_col, A, \
                                    Dskip, xz, ldx, z_col, state, tail, q_start, slot_ids, (T*)out, C, N, L, taps, ws, seg_base, seg_len, seg_slots););
     if (segments <= 1) {
         SCAN_LAUNCH(0, grid);
