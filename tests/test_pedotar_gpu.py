@@ -274,3 +274,42 @@ def test_tensor_core_flexible_attention_against_the_plain_kernel(H, Hkv, da, db,
         assert ops.launch_count - before == 2, "the tensor-core kernel did not take the shape"
         err = (got.float() - want.float()).abs().max().item() / want.float().abs().max().item()
         assert err < 2e-2, f"max_context {max_context}: {err:.3e}"
+
+
+def test_command_line_generates_and_scores(model, tmp_path):
+    """`generate`, `bench` and `ppl` of the command line on a Pedotar model folder: the model class comes from config.json."""
+    import json
+    import math
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, weights = model["cfg"], model["weights"]
+    run = lambda *args: subprocess.run([sys.executable, "-m", "quench6k_b200", *args], cwd=root, capture_output=True, text=True, timeout=600)
+    prompt = helpers.random_tokens(11, cfg["vocab"], 77)
+    r = run("generate", "--model", model["folder"], "--prompt-ids", ",".join(map(str, prompt)), "--n", "6", "--dtype", "float32", "--context", "128")
+    assert r.returncode == 0, r.stderr[-2000:]
+    toks = list(prompt)
+    for _ in range(6):
+        toks.append(int(ph.plain(cfg, weights, toks)[-1].argmax()))
+    assert "prompt: 11 tokens" in r.stdout and f"ids: {toks[11:]}" in r.stdout
+    ids = helpers.random_tokens(72, cfg["vocab"], 78)
+    corpus = tmp_path / "ids.txt"
+    corpus.write_text(" ".join(map(str, ids)))
+    out = tmp_path / "bench.jsonl"
+    r = run("bench", "--model", model["folder"], "--ids", str(corpus), "--ctx", "24", "--generate", "6", "--json", str(out), "--dtype", "float32",
+            "--max-batch-tokens", "10")
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "graph decoding matches eager decoding (6 tokens)" in r.stdout
+    assert [x["ctx"] for x in map(json.loads, out.read_text().splitlines())] == [24]
+    r = run("ppl", "--model", model["folder"], "--file", str(corpus), "--ctx", "24", "--chunks", "3", "--dtype", "float32", "--max-batch-tokens", "7")
+    assert r.returncode == 0, r.stderr[-2000:]
+    nll, count = 0.0, 0
+    for c in range(3):
+        part = ids[c * 24:(c + 1) * 24]
+        logits = ph.plain(cfg, weights, part)
+        for p in range(12, 23):
+            nll += float(torch.logsumexp(logits[p], -1) - logits[p][part[p + 1]])
+            count += 1
+    got = float(r.stdout.strip().splitlines()[-1].split(":")[1].split("(")[0])
+    assert abs(got - math.exp(nll / count)) <= 2e-4 * got, (got, math.exp(nll / count))
