@@ -38,7 +38,12 @@ P3 = {"architecture": "Pedotar", "vocab": 512, "width": 128, "norm": {"eps": 1e-
                  _chunked(8, 8, 16, 16, 100, 0.3)],
       "loop": {"start": 0, "stop": 2, "times": 2}}
 
-ALL = {"P1": P1, "P2": P2, "P3": P3}
+# nothing a multiple of 4: every product, norm and attention on its general path
+P4 = {"architecture": "Pedotar", "vocab": 131, "width": 50, "norm": {"eps": 1e-5}, "kv_page_size": 3,
+      "layers": [_scan(30, 3, 2, 2), _latent(2, 6, 2, 5, 7, 1000.0, 0.4, ff=22), _chunked(2, 1, 6, 10, 9, 0.4)],
+      "loop": {"start": 0, "stop": 3, "times": 2}}
+
+ALL = {"P1": P1, "P2": P2, "P3": P3, "P4": P4}
 
 
 def get(name):

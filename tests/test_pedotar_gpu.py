@@ -119,10 +119,11 @@ def test_a_hidden_key_would_show(single):
 
 
 # ------------------------------------------------------------------------------------------------- whole models
-LENGTHS = {"P1": [71, 130, 45, 96, 64, 33, 1, 58, 77], "P2": [85, 140, 37, 101, 2, 50, 90, 125, 44], "P3": [90, 257, 129, 48, 75, 40, 310, 66, 83]}
+LENGTHS = {"P1": [71, 130, 45, 96, 64, 33, 1, 58, 77], "P2": [85, 140, 37, 101, 2, 50, 90, 125, 44], "P3": [90, 257, 129, 48, 75, 40, 310, 66, 83],
+           "P4": [70, 33, 131, 20, 64, 3, 95, 41, 58]}
 
 
-@pytest.fixture(scope="module", params=["P1", "P2", "P3"])
+@pytest.fixture(scope="module", params=["P1", "P2", "P3", "P4"])
 def model(request, tmp_path_factory):
     name = request.param
     folder = str(tmp_path_factory.mktemp(name))

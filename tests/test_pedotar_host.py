@@ -15,7 +15,7 @@ from quench6k_b200.models.decoder import DecoderModel
 from quench6k_b200.models.pedotar import build_spec
 
 
-@pytest.mark.parametrize("name", ["P1", "P2", "P3"])
+@pytest.mark.parametrize("name", ["P1", "P2", "P3", "P4"])
 def test_config_round_trip_and_order(name, tmp_path):
     d = pedotar_configs.get(name)
     cfg = PedotarConfig.from_dict(d)
