@@ -219,6 +219,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_flex_mma_kernel(const Mm
             for (int e = 0; e < 4; ++e) s[mb][e] = 0.0f;
         const __nv_bfloat16* kb = Ks + (warp * 8 + (lane & 7)) * ldq + ((lane >> 3) & 1) * 8;
         const __nv_bfloat16* qa0 = Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * ldq + (lane >> 4) * 8;
+#pragma unroll 4
         for (int k0 = 0; k0 < dk; k0 += 16) {
             unsigned b0, b1, a0, a1, a2, a3;
             ldmatrix_x2(b0, b1, kb + k0);
