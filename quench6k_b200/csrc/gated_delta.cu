@@ -1,0 +1,257 @@
+// Two things a mixer with per-request state needs, for any mix of prompt portions and single tokens:
+//
+// 1. A short causal convolution over time on every channel of a projection, with the last taps - 1 projected
+//    values of each request kept in its state slot:
+//
+//      y[t, c] = act(sum_j w[c, j] * p[t - taps + 1 + j, c]),   p = projection (+ bias), zeros before the sequence's start
+//
+//    short_conv_kernel computes y from the step's rows and the slot's tail, short_conv_tail_kernel then moves the
+//    tail on.  The projection may come as split-K partial sums, which are added in order.
+//
+// 2. The gated delta rule.  Per head, with a state S [dk, dv] in FP32:
+//
+//      S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+//
+//    with q and k made unit vectors per head first (q also times dk^-1/2), beta = sigmoid(b) and the decay
+//    g = exp(-exp(A_log) softplus(a + dt_bias)), all in FP32.  The columns of S do not meet: column j of S, v, u and o
+//    is a recurrence of its own given q, k, g and beta.  A block owns DELTA_COLS columns of one head of one request;
+//    DELTA_LANES lanes share a column, lane l holding rows l, l + DELTA_LANES, ...; the sums over the rows are
+//    butterflies over those lanes, so their order depends on dk alone.  Tokens of a request are walked in order, so a
+//    prompt cut anywhere leaves the same state, bit for bit, as the whole prompt.  o = S'^T q + (k . q) u uses the
+//    state after the decay, so the two sums over the rows are taken in one pass, before the write.
+//    The state is kept column-major, [slots, heads, dv, dk]: a column's rows lie together.
+//
+//    delta_out_kernel closes the mixer: every head's o is divided by its root mean square over dv, multiplied by a
+//    weight shared by the heads and by silu of a gate projection, and leaves in the operand dtype for the output product.
+#include "common.cuh"
+
+namespace {
+
+constexpr int CONV_MAX_TAPS = 16;
+constexpr int DELTA_LANES = 8;
+constexpr int DELTA_COLS = 16;
+constexpr int DELTA_TILE = 16;       // tokens whose inputs are staged in shared memory at a time
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+// the projected value of row `row`, channel c: the slices in order, then the bias
+__device__ __forceinline__ float projected(const float* x, int slices, size_t slice_stride, int ldx, const float* bias, size_t row, int c) {
+    float v = x[row * ldx + c];
+    for (int s = 1; s < slices; ++s) v += x[s * slice_stride + row * ldx + c];
+    return bias ? v + bias[c] : v;
+}
+
+// grid (T, ceil(C / 256)).  x: FP32 [slices, T, ldx], the convolved channels in its first C columns; the columns from C
+// to `copy_to` pass through (summed, no bias); tail: FP32 [slots, taps-1, C]; out: FP32 [T, ldo].
+__global__ void __launch_bounds__(256) short_conv_kernel(const float* x, int slices, size_t slice_stride, int ldx, const float* bias,
+                                                         const float* w, const float* tail, const int* req_of_token, const int* q_start,
+                                                         const int* slot_ids, float* out, int ldo, int C, int copy_to, int taps, int act) {
+    pdl_enter();
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= copy_to) return;
+    if (c >= C) {
+        out[(size_t)t * ldo + c] = projected(x, slices, slice_stride, ldx, nullptr, t, c);
+        return;
+    }
+    const int r = req_of_token[t], first = q_start[r], i = t - first;
+    const float* old = tail + (size_t)slot_ids[r] * (taps - 1) * C;
+    float acc = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int src = i - (taps - 1 - j);                      // index within the portion; negative: before it
+        const float v = src >= 0 ? projected(x, slices, slice_stride, ldx, bias, first + src, c) : old[(size_t)(taps - 1 + src) * C + c];
+        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+    }
+    out[(size_t)t * ldo + c] = act ? silu_f(acc) : acc;
+}
+
+// grid (R, ceil(C / 256)): the slot's tail becomes the last taps - 1 projected values of the request, this step's rows included.
+__global__ void __launch_bounds__(256) short_conv_tail_kernel(const float* x, int slices, size_t slice_stride, int ldx, const float* bias,
+                                                              float* tail, const int* q_start, const int* slot_ids, int C, int taps) {
+    pdl_enter();
+    const int r = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int first = q_start[r], n = q_start[r + 1] - first;
+    float* mine = tail + (size_t)slot_ids[r] * (taps - 1) * C;
+    float keep[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+        if (j < taps - 1) {
+            const int src = n - (taps - 1) + j;                  // index within the portion; negative: what the tail held
+            keep[j] = src >= 0 ? projected(x, slices, slice_stride, ldx, bias, first + src, c) : mine[(size_t)(taps - 1 + src) * C + c];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+        if (j < taps - 1) mine[(size_t)j * C + c] = keep[j];
+}
+
+// grid (heads * ceil(dv / DELTA_COLS), R), DELTA_COLS * DELTA_LANES threads.  RPL: rows of the state per lane (dk <= RPL * DELTA_LANES).
+// u: FP32 [T, ldu] with q at column 0 (G heads of dk), k after it, v after that (H heads of dv); p: FP32 [T, ldp] with
+// the H beta logits at b_col and the H decay inputs at a_col.
+template <int RPL>
+__global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(const float* u, int ldu, const float* p, int ldp, int b_col, int a_col,
+                                                                              const float* A_log, const float* dt_bias, float* state,
+                                                                              const int* q_start, const int* slot_ids, float* o, int H,
+                                                                              int G, int dk, int dv) {
+    pdl_enter();
+    extern __shared__ float sm[];
+    float* s_k = sm;                                  // [TILE][dk] unit keys
+    float* s_q = s_k + DELTA_TILE * dk;               // [TILE][dk] unit queries times dk^-1/2
+    float* s_v = s_q + DELTA_TILE * dk;               // [TILE][COLS]
+    float* s_beta = s_v + DELTA_TILE * DELTA_COLS;    // [TILE]
+    float* s_g = s_beta + DELTA_TILE;                 // [TILE]
+    float* s_kq = s_g + DELTA_TILE;                   // [TILE]
+    const int col_blocks = (dv + DELTA_COLS - 1) / DELTA_COLS;
+    const int head = blockIdx.x / col_blocks, col0 = (blockIdx.x % col_blocks) * DELTA_COLS, r = blockIdx.y;
+    const int kvh = head / (H / G);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int sub = threadIdx.x % DELTA_LANES, cl = threadIdx.x / DELTA_LANES, col = col0 + cl;
+    const int first = q_start[r], n = q_start[r + 1] - first;
+    const int q_at = kvh * dk, k_at = G * dk + kvh * dk, v_at = 2 * G * dk + head * dv;
+    const float decay_rate = -expf(A_log[head]), bias = dt_bias[head], q_mult = rsqrtf((float)dk);
+    float* mine = state + (((size_t)slot_ids[r] * H + head) * dv + (col < dv ? col : 0)) * dk;
+    float S[RPL];
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+        const int row = sub + DELTA_LANES * i;
+        S[i] = col < dv && row < dk ? mine[row] : 0.0f;
+    }
+    for (int t0 = 0; t0 < n; t0 += DELTA_TILE) {
+        const int nt = min(DELTA_TILE, n - t0);
+        __syncthreads();
+        // the tile's inputs: a warp per token makes the unit vectors, their product, beta and the decay
+        for (int t = warp; t < nt; t += nwarps) {
+            const float* ur = u + (size_t)(first + t0 + t) * ldu;
+            float kk = 0.0f, qq = 0.0f;
+            for (int i = lane; i < dk; i += 32) {
+                const float kv = ur[k_at + i], qv = ur[q_at + i];
+                kk = fmaf(kv, kv, kk), qq = fmaf(qv, qv, qq);
+            }
+            kk = warp_sum(kk), qq = warp_sum(qq);
+            const float k_inv = rsqrtf(kk + 1e-6f), q_inv = rsqrtf(qq + 1e-6f) * q_mult;
+            float dot = 0.0f;
+            for (int i = lane; i < dk; i += 32) {
+                const float kv = ur[k_at + i] * k_inv, qv = ur[q_at + i] * q_inv;
+                s_k[t * dk + i] = kv, s_q[t * dk + i] = qv;
+                dot = fmaf(kv, qv, dot);
+            }
+            dot = warp_sum(dot);
+            if (lane == 0) {
+                const float* pr = p + (size_t)(first + t0 + t) * ldp;
+                s_kq[t] = dot;
+                s_beta[t] = 1.0f / (1.0f + expf(-pr[b_col + head]));
+                s_g[t] = expf(decay_rate * softplus_f(pr[a_col + head] + bias));
+            }
+        }
+        for (int i = threadIdx.x; i < nt * DELTA_COLS; i += blockDim.x) {
+            const int t = i / DELTA_COLS, c = col0 + i % DELTA_COLS;
+            s_v[i] = c < dv ? u[(size_t)(first + t0 + t) * ldu + v_at + c] : 0.0f;
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float g = s_g[t];
+            const float* kr = s_k + t * dk;
+            const float* qr = s_q + t * dk;
+            float kv[RPL], sk = 0.0f, sq = 0.0f;
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                const int row = sub + DELTA_LANES * i;
+                kv[i] = row < dk ? kr[row] : 0.0f;
+                const float qv = row < dk ? qr[row] : 0.0f;
+                S[i] *= g;
+                sk = fmaf(S[i], kv[i], sk), sq = fmaf(S[i], qv, sq);
+            }
+#pragma unroll
+            for (int off = DELTA_LANES / 2; off > 0; off >>= 1) {
+                sk += __shfl_xor_sync(0xffffffffu, sk, off);
+                sq += __shfl_xor_sync(0xffffffffu, sq, off);
+            }
+            const float uu = s_beta[t] * (s_v[t * DELTA_COLS + cl] - sk);
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) S[i] = fmaf(kv[i], uu, S[i]);
+            if (sub == 0 && col < dv) o[(size_t)(first + t0 + t) * H * dv + head * dv + col] = fmaf(s_kq[t], uu, sq);
+        }
+    }
+    if (col < dv) {
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            const int row = sub + DELTA_LANES * i;
+            if (row < dk) mine[row] = S[i];
+        }
+    }
+}
+
+// grid (T, ceil(H / 4)), a warp per (token, head): out = T(o / rms(o) * w * silu(gate)).
+template <typename T>
+__global__ void __launch_bounds__(128) delta_out_kernel(const float* o, const float* p, int ldp, int g_col, const float* w, float eps, T* out,
+                                                        int H, int dv) {
+    pdl_enter();
+    const int t = blockIdx.x, head = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (head >= H) return;
+    const float* orow = o + ((size_t)t * H + head) * dv;
+    const float* grow = p + (size_t)t * ldp + g_col + head * dv;
+    float ss = 0.0f;
+    for (int i = lane; i < dv; i += 32) ss = fmaf(orow[i], orow[i], ss);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)dv + eps);
+    for (int i = lane; i < dv; i += 32) out[((size_t)t * H + head) * dv + i] = from_f32<T>(orow[i] * inv * w[i] * silu_f(grow[i]));
+}
+
+}  // namespace
+
+// out[t, c] = act(short convolution of the projected channel c up to row t) for c < C; columns C..copy_to of x are
+// copied (their slices summed).  act: 0 none, 1 silu.  Then call q6k_short_conv_tail with the same x.
+Q6K_API int q6k_short_conv(const float* x, int slices, long long slice_stride, int ldx, const float* bias, const float* w, const float* tail,
+                           const int* req_of_token, const int* q_start, const int* slot_ids, float* out, int ldo, int T_, int C, int copy_to,
+                           int taps, int act, cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && C > 0 && copy_to >= C && taps >= 1 && taps <= CONV_MAX_TAPS && slices >= 1,
+                "short_conv: bad sizes T=%d C=%d taps=%d (at most %d taps) slices=%d", T_, C, taps, CONV_MAX_TAPS, slices);
+    Q6K_REQUIRE(ldx >= copy_to && ldo >= copy_to && (act == 0 || act == 1), "short_conv: rows of %d and %d for %d columns, act %d", ldx, ldo, copy_to, act);
+    dim3 grid(T_, (copy_to + 255) / 256);
+    Q6K_REQUIRE(grid.y <= 65535, "short_conv: %d channels exceed the grid limit", copy_to);
+    q6k_launch(short_conv_kernel, grid, 256, 0, st, x, slices, (size_t)slice_stride, ldx, bias, w, tail, req_of_token, q_start, slot_ids, out,
+               ldo, C, copy_to, taps, act);
+    return q6k_check_launch("short_conv");
+}
+
+Q6K_API int q6k_short_conv_tail(const float* x, int slices, long long slice_stride, int ldx, const float* bias, float* tail, const int* q_start,
+                                const int* slot_ids, int R, int C, int taps, cudaStream_t st) {
+    if (R == 0 || taps <= 1) return 0;
+    Q6K_REQUIRE(R > 0 && C > 0 && taps <= CONV_MAX_TAPS && slices >= 1, "short_conv_tail: bad sizes R=%d C=%d taps=%d", R, C, taps);
+    q6k_launch(short_conv_tail_kernel, dim3(R, (C + 255) / 256), 256, 0, st, x, slices, (size_t)slice_stride, ldx, bias, tail, q_start, slot_ids,
+               C, taps);
+    return q6k_check_launch("short_conv_tail");
+}
+
+Q6K_API int q6k_gated_delta_max_dim() { return 32 * DELTA_LANES; }
+
+// state: FP32 [slots, H, dv, dk]; o: FP32 [T, H * dv].
+Q6K_API int q6k_gated_delta(const float* u, int ldu, const float* p, int ldp, int b_col, int a_col, const float* A_log, const float* dt_bias,
+                            float* state, const int* q_start, const int* slot_ids, float* o, int R, int H, int G, int dk, int dv,
+                            cudaStream_t st) {
+    if (R == 0) return 0;
+    Q6K_REQUIRE(R > 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, "gated_delta: bad sizes R=%d H=%d G=%d dk=%d dv=%d", R, H, G, dk, dv);
+    Q6K_REQUIRE(dk <= 32 * DELTA_LANES, "gated_delta: keys of %d entries exceed the supported %d", dk, 32 * DELTA_LANES);
+    Q6K_REQUIRE(R <= 65535, "gated_delta: %d requests exceed the grid limit", R);
+    const dim3 grid(H * ((dv + DELTA_COLS - 1) / DELTA_COLS), R);
+    const size_t smem = (size_t)(2 * DELTA_TILE * dk + DELTA_TILE * DELTA_COLS + 3 * DELTA_TILE) * sizeof(float);
+    const int rpl = (dk + DELTA_LANES - 1) / DELTA_LANES;
+#define Q6K_DELTA_GO(RPL_) q6k_launch(gated_delta_kernel<RPL_>, grid, DELTA_COLS * DELTA_LANES, smem, st, u, ldu, p, ldp, b_col, a_col, A_log, dt_bias, state, q_start, slot_ids, o, H, G, dk, dv)
+    if (rpl <= 4) Q6K_DELTA_GO(4);
+    else if (rpl <= 8) Q6K_DELTA_GO(8);
+    else if (rpl <= 16) Q6K_DELTA_GO(16);
+    else Q6K_DELTA_GO(32);
+#undef Q6K_DELTA_GO
+    return q6k_check_launch("gated_delta");
+}
+
+Q6K_API int q6k_delta_out(const float* o, const float* p, int ldp, int g_col, const float* w, float eps, void* out, int T_, int H, int dv, int dtype,
+                          cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && H > 0 && dv > 0, "delta_out: bad sizes T=%d H=%d dv=%d", T_, H, dv);
+    Q6K_REQUIRE((H + 3) / 4 <= 65535, "delta_out: %d heads exceed the grid limit", H);
+    Q6K_DISPATCH(dtype, q6k_launch(delta_out_kernel<T>, dim3(T_, (H + 3) / 4), 128, 0, st, o, p, ldp, g_col, w, eps, (T*)out, H, dv););
+    return q6k_check_launch("delta_out");
+}

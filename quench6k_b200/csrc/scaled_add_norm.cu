@@ -1,0 +1,163 @@
+// The closing add of a block whose sublayers run side by side, and the norms that open the next block, in one pass over
+// the row:
+//
+//   h[t] += m * (a[t] + b[t] + sum_s pw[t, s] * py[row(t, s)])          (each of the three optional)
+//   out1[r] = T(h[t] * rsqrt(mean(h[t]^2) + eps) * w1),  out2[r] likewise with w2    (each optional; t = rows[r] or r)
+//
+// a and b may be split-K partial sums [slices, T, D], added in order.  Everything is FP32; the outputs are in the
+// operand dtype.  One block per row; a thread re-reads only what it wrote itself.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) scaled_add_norm_kernel(float* h, const float* a, int a_slices, const float* b, int b_slices, size_t slice_stride,
+                                                              const float* py, const int* pair_row, const float* pw, int S, float m,
+                                                              const int* rows, const float* w1, T* out1, const float* w2, T* out2, float eps,
+                                                              int D) {
+    pdl_enter();
+    __shared__ float red[32];
+    const int r = blockIdx.x, t = rows ? rows[r] : r;
+    float* hr = h + (size_t)t * D;
+    const bool adds = a || b || py;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = hr[i];
+        if (adds) {
+            float sum = 0.0f;
+            if (a) {
+                sum = a[(size_t)t * D + i];
+                for (int s = 1; s < a_slices; ++s) sum += a[s * slice_stride + (size_t)t * D + i];
+            }
+            if (b) {
+                float sb = b[(size_t)t * D + i];
+                for (int s = 1; s < b_slices; ++s) sb += b[s * slice_stride + (size_t)t * D + i];
+                sum += sb;
+            }
+            if (py) {
+                float sp = 0.0f;
+                for (int s = 0; s < S; ++s) sp = fmaf(pw[t * S + s], py[(size_t)(pair_row ? pair_row[t * S + s] : t * S + s) * D + i], sp);
+                sum += sp;
+            }
+            v = fmaf(m, sum, v);
+            hr[i] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    if (!out1 && !out2) return;
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = hr[i] * inv;
+        if (out1) out1[(size_t)r * D + i] = from_f32<T>(v * w1[i]);
+        if (out2) out2[(size_t)r * D + i] = from_f32<T>(v * w2[i]);
+    }
+}
+
+// act: 0 silu, 1 the tanh form of gelu, 2 the square of relu
+__device__ __forceinline__ float activation(float z, int act) {
+    if (act == 0) return z / (1.0f + expf(-z));
+    if (act == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    const float p = fmaxf(z, 0.0f);
+    return p * p;
+}
+
+// out[r, i] = T(act(x[r, i]) * x[r, I + i]) (gated: x has 2 I columns) or T(act(x[r, i])).
+template <typename T>
+__global__ void activate_kernel(const float* x, int ldx, T* out, int I, size_t count, int gated, int act) {
+    pdl_enter();
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= count) return;
+    const size_t r = idx / I;
+    const int i = (int)(idx % I);
+    const float z = activation(x[r * ldx + i], act);
+    out[idx] = from_f32<T>(gated ? z * x[r * ldx + I + i] : z);
+}
+
+// One warp per token: scores s = sigmoid(logits), the k largest of s + bias (ties to the lower index), weights
+// s / (sum of the chosen s + 1e-20) * scale.  logits: [slices, T, E], summed in order.  Shared memory: E floats a warp (the
+// choice values) and E more (the scores).
+__global__ void route_biased_kernel(const float* logits, int slices, size_t slice_stride, const float* bias, float scale, int T_, int E, int k,
+                                    int* sel_e, float* sel_w) {
+    pdl_enter();
+    extern __shared__ float sc[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int t = blockIdx.x * warps + warp;
+    if (t >= T_) return;
+    float* choice = sc + (size_t)warp * 2 * E;
+    float* score = choice + E;
+    for (int e = lane; e < E; e += 32) {
+        float z = logits[(size_t)t * E + e];
+        for (int s = 1; s < slices; ++s) z += logits[s * slice_stride + (size_t)t * E + e];
+        const float sg = 1.0f / (1.0f + expf(-z));
+        score[e] = sg;
+        choice[e] = bias ? sg + bias[e] : sg;
+    }
+    __syncwarp();
+    float sum = 0.0f, mine = 0.0f;
+    int mine_e = 0;
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float c = choice[e];
+            if (c > best || (c == best && e < best_e)) best = c, best_e = e;       // NaN never wins; taken experts are -inf
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+            if (ob > best || (ob == best && oe < best_e)) best = ob, best_e = oe;
+        }
+        if (best_e >= E) best_e = 0;                                               // every value NaN: a defined answer
+        const float sg = score[best_e];
+        sum += sg;
+        if ((j & 31) == lane) {
+            if (j >= 32) sel_w[(size_t)t * k + j - 32] = mine, sel_e[(size_t)t * k + j - 32] = mine_e;
+            mine = sg, mine_e = best_e;
+        }
+        __syncwarp();
+        if (lane == 0) choice[best_e] = -INFINITY;
+        __syncwarp();
+    }
+    const float den = sum + 1e-20f;
+    // every lane's last result, then the earlier ones it parked in memory
+    const int last = lane < k ? ((k - 1 - lane) >> 5) * 32 + lane : -1;
+    if (last >= 0) sel_w[(size_t)t * k + last] = mine, sel_e[(size_t)t * k + last] = mine_e;
+    __syncwarp();
+    for (int j = lane; j < k; j += 32) sel_w[(size_t)t * k + j] = sel_w[(size_t)t * k + j] / den * scale;
+}
+
+}  // namespace
+
+Q6K_API int q6k_scaled_add_norm(float* h, const float* a, int a_slices, const float* b, int b_slices, long long slice_stride, const float* py,
+                                const int* pair_row, const float* pw, int S, float m, const int* rows, const float* w1, void* out1,
+                                const float* w2, void* out2, float eps, int R, int D, int dtype, cudaStream_t st) {
+    if (R == 0) return 0;
+    Q6K_REQUIRE(R > 0 && D > 0 && a_slices >= 1 && b_slices >= 1, "scaled_add_norm: bad sizes R=%d D=%d", R, D);
+    Q6K_REQUIRE(!(rows && (a || b || py)), "scaled_add_norm: the add takes no row selection");
+    Q6K_REQUIRE(!py || (pw && S > 0), "scaled_add_norm: weighted rows need their weights");
+    Q6K_REQUIRE((out1 == nullptr || w1) && (out2 == nullptr || w2), "scaled_add_norm: an output needs its weight");
+    Q6K_DISPATCH(dtype, q6k_launch(scaled_add_norm_kernel<T>, R, 256, 0, st, h, a, a_slices, b, b_slices, (size_t)slice_stride, py, pair_row, pw, S, m,
+                                   rows, w1, (T*)out1, w2, (T*)out2, eps, D););
+    return q6k_check_launch("scaled_add_norm");
+}
+
+Q6K_API int q6k_activate(const float* x, int ldx, void* out, int rows, int I, int gated, int act, int dtype, cudaStream_t st) {
+    if (rows == 0) return 0;
+    Q6K_REQUIRE(rows > 0 && I > 0 && ldx >= (gated ? 2 * I : I) && act >= 0 && act <= 2, "activate: bad sizes rows=%d I=%d ldx=%d act=%d", rows, I, ldx, act);
+    const size_t count = (size_t)rows * I;
+    Q6K_DISPATCH(dtype, q6k_launch(activate_kernel<T>, (unsigned)((count + 255) / 256), 256, 0, st, x, ldx, (T*)out, I, count, gated, act););
+    return q6k_check_launch("activate");
+}
+
+Q6K_API int q6k_route_biased(const float* logits, int slices, const float* bias, float scale, int T_, int E, int k, int* sel_e, float* sel_w,
+                             cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && E > 0 && k > 0 && k <= E && slices >= 1, "route_biased: bad sizes T=%d E=%d k=%d slices=%d", T_, E, k, slices);
+    Q6K_REQUIRE(E <= 4096, "route_biased: %d experts exceed the supported 4096", E);
+    const int warps = E <= 1024 ? 4 : 1;
+    q6k_launch(route_biased_kernel, (T_ + warps - 1) / warps, warps * 32, (size_t)warps * 2 * E * sizeof(float), st, logits, slices, (size_t)T_ * E, bias,
+               scale, T_, E, k, sel_e, sel_w);
+    return q6k_check_launch("route_biased");
+}

@@ -107,7 +107,7 @@ class ModelRunner:
         arch, cfg = load_config(folder)
         model = DecoderModel(arch.build_spec(cfg))
         rt = Runtime(torch.device(device), parse_dtype(dtype), tensor_cores)
-        get = load_folder(folder, model.tensors(), model.spec.name_alias, device=rt.device)
+        get = load_folder(folder, model.tensors(), model.spec.name_alias, device=rt.device, ignorable=model.spec.ignorable)
         model.bind(get, rt)
         if get.uploader is not None:
             get.uploader.finish()

@@ -35,7 +35,7 @@ class DecoderModel:
                 after["norm1b"] = make_part(NORMS, "norm", ls.post_norm, size=D)
                 if ffn is not None:
                     after["norm2b"] = make_part(NORMS, "norm", ls.post_norm, size=D)
-            self.blocks.append(BLOCKS[ls.block](norm1, mixer, norm2, ffn, **after))
+            self.blocks.append(BLOCKS[ls.block](norm1, mixer, norm2, ffn, **after, **ls.block_params))
         self.final_norm = make_part(NORMS, "norm", spec.final_norm, size=D)
         self.order = list(spec.order)
         self.kv_source = list(spec.kv_source)

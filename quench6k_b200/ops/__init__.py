@@ -1206,3 +1206,151 @@ def attention_flex_tile_tokens(H: int, Hkv: int) -> int:
     lib = library()
     lib.q6k_attention_flex_mma_tile_tokens.restype = ctypes.c_int
     return lib.q6k_attention_flex_mma_tile_tokens(_i(H), _i(Hkv))
+
+
+# --------------------------------------------------------------------------- short convolution, gated delta rule
+def _slices_of(x: torch.Tensor):
+    """(slices, stride between slices in floats, rows, columns) of an FP32 [T, N] matrix or [slices, T, N] partial sums."""
+    if x.dim() == 3:
+        return x.shape[0], x.shape[1] * x.shape[2], x.shape[1], x.shape[2]
+    return 1, 0, x.shape[0], x.shape[1]
+
+
+def short_conv(x: torch.Tensor, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor], tail: torch.Tensor, req_of_token: torch.Tensor,
+               q_start: torch.Tensor, slot_ids: torch.Tensor, R: int, act: Optional[str] = None, copy_to: Optional[int] = None) -> torch.Tensor:
+    """FP32 out[t, c] = act(sum_j w[c, j] * p[t - taps + 1 + j, c]) per request for the first `channels` columns of x, where
+    p = x (+ bias) and the rows before a portion come from tail [slots, taps-1, channels] (the last projected values of the
+    request's earlier portions, zeros at its start); the tail is then moved on by this step's rows.  x: FP32 [T, N] or
+    [slices, T, N] partial sums (added in order).  Columns channels..copy_to of x are copied into the result (summed).
+    act: None or "silu"."""
+    _need(x, "x", torch.float32)
+    slices, stride, T, N = _slices_of(x)
+    taps = w.shape[1]
+    _need(w, "w", torch.float32, (channels, taps))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (channels,))
+    _need(tail, "tail", torch.float32)
+    copy_to = channels if copy_to is None else copy_to
+    if tuple(tail.shape[1:]) != (max(taps - 1, 0), channels) or N < copy_to or copy_to < channels:
+        raise KernelError("short_conv: shapes disagree")
+    if act not in (None, "silu"):
+        raise KernelError(f"short_conv: unknown activation {act!r}")
+    out = torch.empty((T, copy_to), dtype=torch.float32, device=x.device)
+    _call("q6k_short_conv", _ptr(x), _i(slices), _ll(stride), _i(N), _ptr(bias), _ptr(w), _ptr(tail), _ptr(req_of_token), _ptr(q_start),
+          _ptr(slot_ids), _ptr(out), _i(copy_to), _i(T), _i(channels), _i(copy_to), _i(taps), _i(1 if act == "silu" else 0), _stream())
+    if taps > 1:
+        _call("q6k_short_conv_tail", _ptr(x), _i(slices), _ll(stride), _i(N), _ptr(bias), _ptr(tail), _ptr(q_start), _ptr(slot_ids), _i(R),
+              _i(channels), _i(taps), _stream())
+    return out
+
+
+@functools.lru_cache(maxsize=None)
+def gated_delta_max_dim() -> int:
+    lib = library()
+    lib.q6k_gated_delta_max_dim.restype = ctypes.c_int
+    return lib.q6k_gated_delta_max_dim()
+
+
+def gated_delta(u: torch.Tensor, p: torch.Tensor, b_col: int, a_col: int, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
+                q_start: torch.Tensor, slot_ids: torch.Tensor, R: int, H: int, G: int, dk: int, dv: int) -> torch.Tensor:
+    """The gated delta rule over the step's rows, request by request, from and into state [slots, H, dv, dk] (FP32):
+    S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with unit q (times dk^-1/2) and k.  u: FP32 [T, >= 2 G dk + H dv]
+    = [q | k | v]; p: FP32 rows holding the H beta logits at b_col and the H decay inputs at a_col.  Returns FP32 o [T, H dv]."""
+    _need(u, "u", torch.float32)
+    _need(p, "p", torch.float32)
+    _need(A_log, "A_log", torch.float32, (H,))
+    _need(dt_bias, "dt_bias", torch.float32, (H,))
+    _need(state, "state", torch.float32)
+    T = u.shape[0]
+    if tuple(state.shape[1:]) != (H, dv, dk) or u.shape[1] < 2 * G * dk + H * dv or p.shape[0] != T or max(b_col, a_col) + H > p.shape[1]:
+        raise KernelError("gated_delta: shapes disagree")
+    o = torch.empty((T, H * dv), dtype=torch.float32, device=u.device)
+    _call("q6k_gated_delta", _ptr(u), _i(u.stride(0)), _ptr(p), _i(p.stride(0)), _i(b_col), _i(a_col), _ptr(A_log), _ptr(dt_bias), _ptr(state),
+          _ptr(q_start), _ptr(slot_ids), _ptr(o), _i(R), _i(H), _i(G), _i(dk), _i(dv), _stream())
+    return o
+
+
+def delta_out(o: torch.Tensor, p: torch.Tensor, g_col: int, w: torch.Tensor, eps: float, H: int, dv: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """out_dtype(o / rms(o) * w * silu(gate)) per (row, head): o FP32 [T, H dv], the gate in p's columns from g_col on."""
+    _need(o, "o", torch.float32)
+    _need(p, "p", torch.float32)
+    _need(w, "w", torch.float32, (dv,))
+    T = o.shape[0]
+    if o.shape[1] != H * dv or p.shape[0] != T or g_col + H * dv > p.shape[1]:
+        raise KernelError("delta_out: shapes disagree")
+    out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
+    _call("q6k_delta_out", _ptr(o), _ptr(p), _i(p.stride(0)), _i(g_col), _ptr(w), _f(eps), _ptr(out), _i(T), _i(H), _i(dv), _i(dtype_code(out_dtype)),
+          _stream())
+    return out
+
+
+# --------------------------------------------------------------------------- a block of sublayers side by side
+def scaled_add_norm(h: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], weighted, scale: float, w1: Optional[torch.Tensor],
+                    w2: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
+    """h += scale * (a + b + weighted rows) in place (each optional; a and b FP32 [T, D] or [slices, T, D] partial sums, weighted =
+    (y, pair_row, weights) as in `combine`), then (out1, out2) = h * rsqrt(mean(h^2) + eps) * (w1, w2) in out_dtype for the
+    weights given (None otherwise).  rows: normalise these rows only (no add then)."""
+    _need(h, "h", torch.float32)
+    T, D = h.shape
+    stride = T * D
+    counts = []
+    for name, t in (("a", a), ("b", b)):
+        if t is None:
+            counts.append(1)
+            continue
+        _need(t, name, torch.float32)
+        if tuple(t.shape[-2:]) != (T, D):
+            raise KernelError(f"scaled_add_norm: {name} does not match h")
+        counts.append(t.shape[0] if t.dim() == 3 else 1)
+    y = pair_row = pair_w = None
+    S = 0
+    if weighted is not None:
+        y, pair_row, pair_w = weighted
+        S = pair_w.shape[1]
+        _need(y, "weighted rows", torch.float32)
+        _need(pair_w, "weights", torch.float32)
+        if pair_row is not None:
+            _need(pair_row, "pair_row", torch.int32)
+        if pair_w.shape[0] != T or y.shape[1] != D or y.shape[0] < T * S:
+            raise KernelError("scaled_add_norm: the weighted rows do not match h")
+    R = T if rows is None else rows.numel()
+    outs = []
+    for w in (w1, w2):
+        if w is not None:
+            _need(w, "w", torch.float32, (D,))
+            outs.append(torch.empty((R, D), dtype=out_dtype, device=h.device))
+        else:
+            outs.append(None)
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _call("q6k_scaled_add_norm", _ptr(h), _ptr(a), _i(counts[0]), _ptr(b), _i(counts[1]), _ll(stride), _ptr(y), _ptr(pair_row), _ptr(pair_w), _i(S),
+          _f(scale), _ptr(rows), _ptr(w1), _ptr(outs[0]), _ptr(w2), _ptr(outs[1]), _f(eps), _i(R), _i(D), _i(dtype_code(out_dtype)), _stream())
+    return outs[0], outs[1]
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+
+
+def activate(x: torch.Tensor, I: int, gated: bool, act: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """out_dtype(act(x[:, :I]) * x[:, I:2 I]) when gated, else out_dtype(act(x[:, :I])); x FP32."""
+    _need(x, "x", torch.float32)
+    if act not in ACTIVATIONS:
+        raise KernelError(f"activate: unknown activation {act!r}")
+    out = torch.empty((x.shape[0], I), dtype=out_dtype, device=x.device)
+    _call("q6k_activate", _ptr(x), _i(x.stride(0)), _ptr(out), _i(x.shape[0]), _i(I), _i(1 if gated else 0), _i(ACTIVATIONS[act]),
+          _i(dtype_code(out_dtype)), _stream())
+    return out
+
+
+def route_biased(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor], scale: float):
+    """(sel_e int32 [T, k], sel_w float32 [T, k]): per row the k experts with the largest sigmoid(logit) + bias (ties to the
+    lower index); weights sigmoid(logit) / (their sum + 1e-20) * scale.  logits: [T, E] or [slices, T, E] partial sums."""
+    _need(logits, "logits", torch.float32)
+    slices = logits.shape[0] if logits.dim() == 3 else 1
+    T, E = logits.shape[-2:]
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (E,))
+    sel_e = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    sel_w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    _call("q6k_route_biased", _ptr(logits), _i(slices), _ptr(bias), _f(scale), _i(T), _i(E), _i(k), _ptr(sel_e), _ptr(sel_w), _stream())
+    return sel_e, sel_w

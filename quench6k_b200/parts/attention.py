@@ -5,7 +5,10 @@ operations, crates/cuda/kernels/flint.cu:125-173 and :211-561 for the arithmetic
 Beyond the reference: values of another width than the keys (v_dim), a given score scale, a mask of chunks (a position
 sees the earlier positions of its own block of `chunk` positions, blocks counted from position 0), and the heads'
 softmax weights mixed by a learned [heads, heads] matrix before they meet the values (`talk`).  Layers that use any of
-these run the flexible attention kernels; the others run as before."""
+these run the flexible attention kernels; the others run as before.  Two more options change what enters the attention,
+not the attention: biases on the q, k and v projections, and a short causal convolution over time on every channel of
+the projected q, k and v (before normalisation and rotation), whose last taps - 1 inputs are kept per request in a state
+slot so that a prompt may be cut anywhere."""
 from __future__ import annotations
 
 import math
@@ -26,7 +29,7 @@ class Attention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, eps: float,
                  pos: PartSpec, window: Optional[int] = None, sinks: bool = False, qk_norm: bool = False,
                  norm_init: str = "ones", sink_std: float = 1.0, v_dim: Optional[int] = None, scale: Optional[float] = None,
-                 chunk: Optional[int] = None, talk: bool = False, names=None):
+                 chunk: Optional[int] = None, talk: bool = False, names=None, bias: bool = False, conv: Optional[int] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
         self.D, self.Hq, self.Hkv, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
@@ -37,7 +40,10 @@ class Attention(Mixer):
         self.pos = make_part(POSITION_ENCODINGS, "position encoding", pos)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         # the flexible kernels: any widths, chunks, mixed heads; the fixed-shape kernels: everything the reference has
-        self.flexible = self.vd != head_dim or self.chunk is not None or self.talk
+        self.flexible = self.vd != head_dim or self.chunk is not None or self.talk or ((head_dim % 16 != 0 or head_dim > 256) and not sinks)
+        self.has_bias, self.taps = bool(bias), (int(conv) if conv else 0)
+        if self.taps > 16:
+            raise ValueError(f"{self.taps} convolution taps: the kernel takes 1 to 16")
         if self.flexible and sinks:
             raise ValueError("sinks are not combined with chunks, mixed heads or values of another width")
         if self.flexible and self.pos.rotary_table() is None and not self.pos.is_identity:
@@ -48,7 +54,8 @@ class Attention(Mixer):
             raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
         # the tensors' names relative to the part's prefix (an architecture may call them anything)
         self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "q_norm": "q_norm.weight",
-                      "k_norm": "k_norm.weight", "sinks": "sinks", "talk": "talk.weight", **(names or {})}
+                      "k_norm": "k_norm.weight", "sinks": "sinks", "talk": "talk.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias",
+                      "v_bias": "v_proj.bias", "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight", **(names or {})}
 
     def tensors(self):
         D, Hq, Hkv, hd, n = self.D, self.Hq, self.Hkv, self.hd, self.names
@@ -61,6 +68,11 @@ class Attention(Mixer):
             out.append(TensorSpec(n["sinks"], (Hq,), "f32", ("normal", self.sink_std)))
         if self.talk:
             out.append(TensorSpec(n["talk"], (Hq, Hq), "f32", ("normal", 0.5)))
+        widths = (("q", Hq * hd), ("k", Hkv * hd), ("v", Hkv * self.vd))
+        if self.has_bias:
+            out += [TensorSpec(n[x + "_bias"], (c,), "f32", ("normal", 0.1)) for x, c in widths]
+        if self.taps:
+            out += [TensorSpec(n[x + "_conv"], (c, self.taps), "f32", ("normal", 0.5)) for x, c in widths]
         out += [TensorSpec("position." + t.name, t.shape, t.role, t.init) for t in self.pos.tensors()]
         return out
 
@@ -78,6 +90,12 @@ class Attention(Mixer):
         self.k_norm = to_f32(get(n["k_norm"]), rt) if self.qk_norm else None
         self.sinks = to_f32(get(n["sinks"]), rt) if self.has_sinks else None
         self.w_talk = to_f32(get(n["talk"]), rt) if self.talk else None
+        # biases and taps of q, k and v side by side, like the rows of the stacked product
+        self.bias = torch.cat([to_f32(get(n[x + "_bias"]), rt) for x in "qkv"]).contiguous() if self.has_bias else None
+        self.conv_w = torch.cat([to_f32(get(n[x + "_conv"]), rt) for x in "qkv"]).contiguous() if self.taps else None
+        if self.has_bias and not self.taps:                         # a bias alone: one tap of weight one
+            self.conv_w = torch.ones((nq + nk + nv, 1), dtype=torch.float32, device=rt.device)
+        self._no_tail = torch.zeros((1, 0, nq + nk + nv), dtype=torch.float32, device=rt.device)
         self.pos.bind(lambda name: get("position." + name), rt)
 
     def cache_request(self):
@@ -88,12 +106,27 @@ class Attention(Mixer):
             return CacheRequest("sliding", int(self.window), self.Hkv, self.hd, v)
         return CacheRequest("full", None, self.Hkv, self.hd, v)
 
-    def _forward_flexible(self, xn, ctx, cache):
+    def state_shape(self):
+        if self.taps > 1:
+            return {"conv": ((self.taps - 1, self.Hq * self.hd + self.Hkv * (self.hd + self.vd)), torch.float32)}
+        return None
+
+    def _after_projection(self, qkv, ctx, cache, state):
+        """Bias and short convolution on the projected q, k and v (FP32, possibly split-K partial sums): FP32 [T, q | k | v]."""
+        if self.conv_w is None:
+            return qkv
+        if not cache.write:
+            raise ValueError("a layer that borrows another's keys cannot convolve its own")
+        ops.current_tag = "attention.conv"
+        tail = state["conv"] if self.taps > 1 else self._no_tail
+        return ops.short_conv(qkv, self.conv_w.shape[0], self.conv_w, self.bias, tail, ctx.req_of_token, ctx.q_start, ctx.slot_ids, ctx.R)
+
+    def _forward_flexible(self, xn, ctx, cache, state=None):
         """Any key and value widths, a window and/or chunks, mixed heads: the flexible kernels."""
         rt, write = self.rt, cache.write
         table = ctx.block_tables[cache.group]
         ops.current_tag = "attention.qkv"
-        qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=True)
+        qkv = self._after_projection(linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=True), ctx, cache, state)
         ops.current_tag = "attention.prepare"
         q = ops.qkv_pages(qkv, self.Hq, self.Hkv, self.hd, self.vd, self.q_norm, self.k_norm, self.eps, self.pos.rotary_table(),
                           ctx.positions, ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
@@ -103,11 +136,11 @@ class Attention(Mixer):
         a = ops.attention_flex(None, q.view(-1, self.hd), False, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.Hq,
                                self.scale, window=self.window, chunk=self.chunk, talk=self.w_talk, tiles=tiles, max_context=ctx.max_context)
         ops.current_tag = "attention.o"
-        return linear.matmul(a, self.w_o, rt, partials_ok=True)
+        return linear.matmul(a, self.w_o, rt, partials_ok=not ctx.hold_results)
 
     def forward(self, xn, ctx, cache, state, out):
         if self.flexible:
-            return self._forward_flexible(xn, ctx, cache)
+            return self._forward_flexible(xn, ctx, cache, state)
         rt = self.rt
         write = cache.write
         # which attention kernels this step takes, and the plan of the key splits, before anything of the layer is
@@ -118,11 +151,11 @@ class Attention(Mixer):
         fused_pos = rotary is not None or self.pos.is_identity
         # a step of a few tokens per request: the kernel that splits the keys normalises and rotates q itself and makes
         # the new keys and values (one launch less)
-        in_attention = (self.prepare_in_attention and how[0] == "split" and fused_pos and
+        in_attention = (self.prepare_in_attention and how[0] == "split" and fused_pos and self.conv_w is None and
                         ops.attention_mma_prepares(self.hd, self.Hq // self.Hkv, how[1][0], rotary[1] if rotary else 0, bool(rotary and rotary[2])))
         # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]; for few rows possibly as split-K partials, which the next kernel sums
         ops.current_tag = "attention.qkv"
-        qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=fused_pos)
+        qkv = self._after_projection(linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=fused_pos), ctx, cache, state)
         table = ctx.block_tables[cache.group]
         if in_attention:
             ops.current_tag = "attention.keys"
@@ -130,7 +163,7 @@ class Attention(Mixer):
                                  prepare={"qkv": qkv, "heads": self.Hq, "q_norm": self.q_norm, "k_norm": self.k_norm, "eps": self.eps,
                                           "rotary": rotary, "write": write})
             ops.current_tag = "attention.o"
-            return linear.matmul(a, self.w_o, rt, partials_ok=True)
+            return linear.matmul(a, self.w_o, rt, partials_ok=not ctx.hold_results)
         ops.current_tag = "attention.prepare"
         if not fused_pos:
             qkv = self._unfused_position(qkv, ctx, write)
@@ -145,7 +178,7 @@ class Attention(Mixer):
         a = self._attend(q, cache, table, ctx, how)
         # the block adds it into the stream inside its next norm (which also sums split-K partials)
         ops.current_tag = "attention.o"
-        return linear.matmul(a, self.w_o, rt, partials_ok=True)
+        return linear.matmul(a, self.w_o, rt, partials_ok=not ctx.hold_results)
 
     prepare_in_attention = True   # the kernel that splits the keys makes q and the new keys itself where it can (else qk_prep does)
     tc_min_fill = 0.5             # the tcgen05 prompt kernel runs when its CTAs (two tiles each) cover at least this share of the SMs

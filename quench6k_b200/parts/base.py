@@ -116,6 +116,22 @@ class PostNormed:
         self.norm.add_normed(h, self.y)
 
 
+@dataclass
+class ScaledSum:
+    """A residual add that has not been made yet: h += scale * (a + b + weighted rows), what a block whose sublayers run
+    side by side leaves to the norms that open the next block (or to the model's last norm).  a, b: FP32 [T, D] or
+    [slices, T, D] partial sums to be added in order, or None."""
+    scale: float
+    a: Optional[torch.Tensor] = None
+    b: Optional[torch.Tensor] = None
+    weighted: Optional[WeightedRows] = None
+
+    def apply(self, h: torch.Tensor) -> None:
+        from .. import ops
+        w = self.weighted
+        ops.scaled_add_norm(h, self.a, self.b, None if w is None else (w.y, w.pair_row, w.weights), self.scale, None, None, 0.0, torch.float32)
+
+
 class Tap:
     """A debugging aid: a part that is given a Tap copies small per-row results of every forward
     into it (the routed experts: each row's chosen experts and its router logits), one static

@@ -3,7 +3,8 @@ the residual stream h staying FP32 (reference: crates/engine/src/flint.rs:815-10
 from __future__ import annotations
 
 from .. import ops
-from .base import Block, PostNormed, WeightedRows, register_block
+from .base import Block, PostNormed, ScaledSum, WeightedRows, register_block
+from .norm import RMSNorm
 
 
 @register_block("prenorm")
@@ -41,3 +42,52 @@ class SandwichBlock(Block):
         ops.current_tag = "norm.ffn"
         xn = self.norm2.forward(h, add=PostNormed(y, self.norm1b))
         return PostNormed(self.ffn.compute(xn, ctx), self.norm2b)
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """Mixer and feed-forward side by side, each behind a norm of its own, both reading the same stream:
+    h += scale * (mixer(norm1(h)) + ffn(norm2(h))); a block without a feed-forward adds the mixer alone.  The add is left
+    to the next block (or the model's last norm); with RMS norms of one eps, one kernel makes the add the block before has
+    left and both norms in one pass over the row."""
+
+    def __init__(self, norm1, mixer, norm2, ffn, scale: float = 1.0, **after):
+        super().__init__(norm1, mixer, norm2, ffn, **after)
+        self.scale = float(scale)
+
+    def forward(self, h, ctx, cache, state, pending=None):
+        ops.current_tag = "norm.both"
+        n1, n2 = self.norm1, self.norm2
+        fused = isinstance(n1, RMSNorm) and (n2 is None or (isinstance(n2, RMSNorm) and n2.eps == n1.eps))
+        if fused:
+            if pending is not None and not isinstance(pending, ScaledSum):
+                pending.apply(h)
+                pending = None
+            p = pending or ScaledSum(0.0)
+            w = p.weighted
+            x1, x2 = ops.scaled_add_norm(h, p.a, p.b, None if w is None else (w.y, w.pair_row, w.weights), p.scale, n1.weight,
+                                         n2.weight if n2 is not None else None, n1.eps, n1.rt.dtype)
+        else:
+            if pending is not None:
+                pending.apply(h)
+            x1 = n1.forward(h)
+            x2 = n2.forward(h) if n2 is not None else None
+        ctx.hold_results = self.ffn is not None           # the mixer's result waits while the feed-forward runs
+        y = self.mixer.forward(x1, ctx, cache, state, None)
+        ctx.hold_results = False
+        if y is None:
+            raise TypeError(f"{type(self.mixer).__name__} adds into the stream itself; this arrangement needs its result")
+        if self.ffn is None:
+            return ScaledSum(self.scale, y)
+        if hasattr(self.ffn, "compute"):
+            return ScaledSum(self.scale, y, self.ffn.compute(x2, ctx))
+        if self.ffn.defers_add:
+            acc = None
+            rows = self.ffn.forward(x2, ctx, None, defer=True) if getattr(self.ffn, "always_defers", False) else None
+            if rows is None:
+                acc = h.new_zeros(h.shape)
+                rows = self.ffn.forward(x2, ctx, acc, defer=True)
+            return ScaledSum(self.scale, y, acc, rows)
+        acc = h.new_zeros(h.shape)
+        self.ffn.forward(x2, ctx, acc)
+        return ScaledSum(self.scale, y, acc)

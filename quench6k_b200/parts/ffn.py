@@ -10,18 +10,24 @@ part, added after the routed sum.
 from __future__ import annotations
 
 
+import torch
+
 from .. import ops
 from ..spec import TensorSpec
 from . import linear
-from .base import FeedForward, WeightedRows, register_feed_forward, to_operand
+from .base import FeedForward, WeightedRows, register_feed_forward, to_f32, to_operand
 
 
 @register_feed_forward("dense")
 class DenseSwiGLU(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, names=None):
-        self.D, self.I = hidden_size, intermediate_size
+    def __init__(self, hidden_size: int, intermediate_size: int, names=None, act: str = "silu"):
+        """act: what the gate passes through, "silu" (the epilogue of the gate/up product) or another of ops.ACTIVATIONS
+        (then gate and up are one product and the gating a kernel of its own)."""
+        if act not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {act!r}; known: {', '.join(ops.ACTIVATIONS)}")
+        self.D, self.I, self.act = hidden_size, intermediate_size, act
         # the tensors' names relative to the part's prefix (an architecture may call them anything)
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
 
@@ -31,19 +37,31 @@ class DenseSwiGLU(FeedForward):
 
     def bind(self, get, rt):
         self.rt = rt
-        self.w_gate, self.w_up = to_operand(get(self.names["gate"]), rt), to_operand(get(self.names["up"]), rt)
+        if self.act == "silu":
+            self.w_gate, self.w_up = to_operand(get(self.names["gate"]), rt), to_operand(get(self.names["up"]), rt)
+        else:                                                       # gate and up stacked: one product yields [gate | up] per token
+            self.w_gate_up = torch.empty((2 * self.I, self.D), dtype=rt.dtype, device=rt.device)
+            self.w_gate_up[:self.I].copy_(get(self.names["gate"]))
+            self.w_gate_up[self.I:].copy_(get(self.names["up"]))
+            self.w_gate, self.w_up = self.w_gate_up[:self.I], self.w_gate_up[self.I:]
         self.w_down = to_operand(get(self.names["down"]), rt)
 
-    def forward(self, xn, ctx, out):
+    def _gated(self, xn):
         ops.current_tag = "dense.gate_up"
-        act = linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt)
+        if self.act == "silu":
+            return linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt)
+        gu = linear.matmul(xn, self.w_gate_up, self.rt)
+        ops.current_tag = "dense.act"
+        return ops.activate(gu, self.I, True, self.act, self.rt.dtype)
+
+    def forward(self, xn, ctx, out):
+        act = self._gated(xn)
         ops.current_tag = "dense.down"
         linear.matmul(act, self.w_down, self.rt, out=out, accumulate=True)
 
     def compute(self, xn, ctx):
         """The result itself, FP32 [T, D] (or split-K slices of it), for a block whose norm takes it before the stream does."""
-        ops.current_tag = "dense.gate_up"
-        act = linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt)
+        act = self._gated(xn)
         ops.current_tag = "dense.down"
         return linear.matmul(act, self.w_down, self.rt, partials_ok=True)
 
@@ -53,7 +71,20 @@ class RoutedExperts(FeedForward):
     graph_safe = True
 
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int, scoring: str = "softmax",
-                 renormalize: bool = True, shared_intermediate_size: int = 0):
+                 renormalize: bool = True, shared_intermediate_size: int = 0, gated: bool = True, act: str = "silu",
+                 correction: bool = False, route_scale: float = 1.0, names=None):
+        """gated: an expert is down(act(gate x) * (up x)); else down(act(up x)).  correction: a stored vector added to the
+        scores for the choice of the experts only (the weights use the scores without it); route_scale multiplies the
+        weights.  Both belong to sigmoid scoring with renormalised weights."""
+        if act not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {act!r}; known: {', '.join(ops.ACTIVATIONS)}")
+        self.gated, self.act, self.has_correction, self.route_scale = bool(gated), act, bool(correction), float(route_scale)
+        self.own_router = self.has_correction or self.route_scale != 1.0
+        if self.own_router and not (scoring == "sigmoid" and renormalize):
+            raise ValueError("a correction of the choice and a scale of the weights go with sigmoid scores and renormalised weights")
+        self.fused_act = self.gated and act == "silu"
+        self.names = {"router": "gate.weight", "gate": "experts.gate_proj.weight", "up": "experts.up_proj.weight",
+                      "down": "experts.down_proj.weight", "correction": "gate.correction", **(names or {})}
         if scoring not in ("softmax", "sigmoid"):
             raise ValueError(f"unknown router scoring {scoring!r}")
         if not 0 < top_k <= num_experts:
@@ -61,23 +92,30 @@ class RoutedExperts(FeedForward):
         self.D, self.E, self.k, self.I = hidden_size, num_experts, top_k, intermediate_size
         self.scoring, self.renorm = scoring, bool(renormalize)
         self.shared = DenseSwiGLU(hidden_size, shared_intermediate_size) if shared_intermediate_size > 0 else None
+        self.always_defers = self.shared is None      # forward(defer=True) never touches `out`
         self.routing_tap = None               # a parts.base.Tap: every forward records each row's chosen experts [T, k]
                                               # ("experts") and its router logits [T, E] ("router_logits") there
 
     def tensors(self):
-        E, I, D = self.E, self.I, self.D
-        out = [TensorSpec("gate.weight", (E, D)), TensorSpec("experts.gate_proj.weight", (E, I, D)),
-               TensorSpec("experts.up_proj.weight", (E, I, D)), TensorSpec("experts.down_proj.weight", (E, D, I))]
+        E, I, D, n = self.E, self.I, self.D, self.names
+        out = [TensorSpec(n["router"], (E, D))]
+        if self.gated:
+            out.append(TensorSpec(n["gate"], (E, I, D)))
+        out += [TensorSpec(n["up"], (E, I, D)), TensorSpec(n["down"], (E, D, I))]
+        if self.has_correction:
+            out.append(TensorSpec(n["correction"], (E,), "f32", ("normal", 0.1)))
         if self.shared is not None:
             out += [TensorSpec("shared_experts." + t.name, t.shape, t.role, t.init) for t in self.shared.tensors()]
         return out
 
     def bind(self, get, rt):
         self.rt = rt
-        self.w_router = to_operand(get("gate.weight"), rt)
-        self.w_gate = to_operand(get("experts.gate_proj.weight"), rt)
-        self.w_up = to_operand(get("experts.up_proj.weight"), rt)
-        self.w_down = to_operand(get("experts.down_proj.weight"), rt)
+        n = self.names
+        self.w_router = to_operand(get(n["router"]), rt)
+        self.w_up = to_operand(get(n["up"]), rt)
+        self.w_gate = to_operand(get(n["gate"]), rt) if self.gated else self.w_up      # ungated: the first (only) product's weights
+        self.w_down = to_operand(get(n["down"]), rt)
+        self.correction = to_f32(get(n["correction"]), rt) if self.has_correction else None
         if self.shared is not None:
             self.shared.bind(lambda n: get("shared_experts." + n), rt)
 
@@ -99,7 +137,7 @@ class RoutedExperts(FeedForward):
         T = xn.shape[0]
         pairs = T * self.k
         defer = defer and self.shared is None
-        if (rt.tensor_cores and not rt.is_fp32 and ops.router_small_supported(T, self.E, self.D, self.k)
+        if (self.fused_act and not self.own_router and rt.tensor_cores and not rt.is_fp32 and ops.router_small_supported(T, self.E, self.D, self.k)
                 and ops.tc_supported(xn, self.w_gate) and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per
             # (token, slot) pair straight from the selection, no permutation and no gather
@@ -125,13 +163,24 @@ class RoutedExperts(FeedForward):
             return None
         ops.current_tag = "experts.router"
         logits = linear.matmul(xn, self.w_router, rt, partials_ok=True)    # FP32 [T, E], or split-K slices of it that route() sums
-        sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
+        if self.own_router:
+            sel_e, sel_w = ops.route_biased(logits, self.k, self.correction, self.route_scale)
+        else:
+            sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
         if self.routing_tap is not None:
             self._tap(ctx, sel_e, logits)
         ops.current_tag = "experts.permute"
         plan = linear.group_plan(xn, self.w_gate, sel_e, rt)             # permutation by expert, row tiles, gathered rows
         ops.current_tag = "experts.gate_up"
-        act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                         # [pairs, I]
+        if self.fused_act:
+            act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                     # [pairs, I]
+        else:
+            first = linear.grouped_first(xn, plan, self.w_up, rt)                                 # FP32 [pairs, I]
+            if self.gated:
+                gate = linear.grouped_first(xn, plan, self.w_gate, rt)
+                first = torch.cat([gate, first], dim=1)
+            ops.current_tag = "experts.act"
+            act = ops.activate(first, self.I, self.gated, self.act, rt.dtype)
         ops.current_tag = "experts.down"
         y = linear.grouped_matmul(act, plan, self.w_down, rt)                                     # FP32 [pairs, D]
         if defer:

@@ -81,6 +81,14 @@ def grouped_swiglu(a: torch.Tensor, plan: GroupPlan, w_gate: torch.Tensor, w_up:
     return ops.gemm_simt(a, w_gate, w2=w_up, a_rows=plan.row_token, groups=plan.tiles, rows=plan.pairs)
 
 
+def grouped_first(a: torch.Tensor, plan: GroupPlan, w: torch.Tensor, rt) -> torch.Tensor:
+    """FP32 y[row] = a[row_token[row]] @ w_g^T with the weights of the row's group: the experts' first product without an
+    activation in its epilogue; [pairs, N]."""
+    if plan.tc:
+        return ops.gemm_tc(plan.xs, w, groups=plan.tiles, bt=plan.bt, rows=plan.pairs)
+    return ops.gemm_simt(a, w, a_rows=plan.row_token, groups=plan.tiles, rows=plan.pairs)
+
+
 def grouped_matmul(a: torch.Tensor, plan: GroupPlan, w: torch.Tensor, rt) -> torch.Tensor:
     """FP32 y[row] = a[row] @ w_g^T with the weights of the row's group; [pairs, N]."""
     if plan.tc and ops.tc_supported(a, w):

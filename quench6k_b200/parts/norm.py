@@ -11,16 +11,21 @@ from .base import Norm, PostNormed, WeightedRows, register_norm, to_f32
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, size: int, eps: float, init: str = "ones"):
+    def __init__(self, size: int, eps: float, init: str = "ones", weight_name: str = "weight", offset: float = 0.0):
+        """offset: the stored weight is the multiplier minus this (1.0: a weight kept around zero); the sum is made once, in
+        FP32, when the weight is bound.  weight_name: the tensor's name relative to the norm's prefix."""
         self.size, self.eps, self.init = size, float(eps), init
+        self.weight_name, self.offset = weight_name, float(offset)
 
     def tensors(self):
-        init = ("ones",) if self.init == "ones" else ("ones_plus", 0.1)
-        return [TensorSpec("weight", (self.size,), "f32", init)]
+        init = {"ones": ("ones",), "zeros": ("normal", 0.0)}.get(self.init, ("normal", 0.1) if self.offset else ("ones_plus", 0.1))
+        return [TensorSpec(self.weight_name, (self.size,), "f32", init)]
 
     def bind(self, get, rt):
         self.rt = rt
-        self.weight = to_f32(get("weight"), rt)
+        self.weight = to_f32(get(self.weight_name), rt)
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     fuses_weighted_rows = True
 

@@ -26,6 +26,7 @@ class LayerSpec:
     norm: PartSpec              # the kind of both norms of the block
     block: str = "prenorm"      # arrangement, a key of parts.BLOCKS
     post_norm: Optional[PartSpec] = None    # the kind of the norms on the sublayers' results, in arrangements that have them
+    block_params: Dict[str, Any] = field(default_factory=dict)   # constants of the arrangement (a multiplier on what it adds, ...)
 
 
 @dataclass
@@ -42,6 +43,7 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     init_std: float = 0.02                 # std of the random-weights mode for matrices
     name_alias: Optional[Callable[[str], Optional[str]]] = None   # a stored tensor's other name -> the name declared here (or None)
+    ignorable: Optional[Callable[[str], bool]] = None    # stored tensors that may be there without being declared
     # what follows a layer's prefix for each of its parts (a part's own tensor names come after it)
     sub_names: Dict[str, str] = field(default_factory=lambda: {"norm1": "input_layernorm.", "mixer": "self_attn.",
                                                                 "norm2": "post_attention_layernorm.", "ffn": "mlp."})

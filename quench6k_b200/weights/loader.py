@@ -109,7 +109,8 @@ class Uploader:
 
 
 def load_folder(folder: str, declared: List[TensorSpec],
-                alias: Optional[Callable[[str], object]] = None, device=None) -> Callable[[str], torch.Tensor]:
+                alias: Optional[Callable[[str], object]] = None, device=None,
+                ignorable: Optional[Callable[[str], bool]] = None) -> Callable[[str], torch.Tensor]:
     """Check the folder's tensors against the declaration; return `get(name) -> tensor` that reads
     one tensor at a time (so that a large model never sits in host memory whole).  With `device`
     (a CUDA device) the tensors come back on it, streamed through two pinned staging buffers;
@@ -119,9 +120,14 @@ def load_folder(folder: str, declared: List[TensorSpec],
     architecture's table of other naming schemes): the declared name, or (declared name, i) for a
     tensor that is slice i along the first axis of the declared one (experts stored one by one are
     stacked as they are read).  A tensor under another name may also be stored with its leading
-    dimensions flattened ([E*I, D] for a declared [E, I, D]) and is reshaped when read."""
+    dimensions flattened ([E*I, D] for a declared [E, I, D]) and is reshaped when read.
+
+    ignorable: stored tensors that are not declared and for which it returns True are left alone (a file may hold
+    a tensor of a part that this configuration switches off)."""
     index = index_folder(folder)
     want = {s.name: s for s in declared}
+    if ignorable is not None:
+        index = {n: v for n, v in index.items() if n in want or not ignorable(n)}
     stored_as: Dict[str, str] = {}                       # declared (or unknown) name -> name in the files
     slices: Dict[str, Dict[int, str]] = {}               # declared name -> slice index -> name in the files
     wrong: List[str] = []
