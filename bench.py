@@ -281,8 +281,37 @@ def flint_dense_config(size):
             "intermediate_size": ff, "kv_page_size": 16}
 
 
+def kipedra_config(size):
+    """Kipedra at layer sizes that resemble a real model's: a gated delta rule layer with a dense feed-forward, two layers of
+    windowed attention with routed experts and a delta layer with routed experts; the four run twice."""
+    D, ff, heads, kv, E, top, eff, window = {"s": (1024, 4096, 8, 2, 32, 4, 512, 1024), "m": (2048, 8192, 16, 4, 64, 4, 1024, 2048)}[size]
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top, "scale": 2.0}}
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "conv": 4}}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5, "mask": {"size": window},
+                     "rot": {"base": 10000.0, "dims": 64}}}
+    return {"architecture": "Kipedra", "vocab": 32768, "width": D, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "kv_page_size": 16,
+            "layers": [dict(delta, mlp={"kind": "dense", "ff": ff}), att, dict(att), dict(delta, mlp=moe)],
+            "loop": {"start": 0, "stop": 4, "times": 2}}
+
+
+def flint_routed_config(size):
+    """The closest existing model at equal size: Flint with a window on every layer, two dense layers and six with routed
+    experts: the same width, heads, window, experts (count, choice, width), vocabulary and number of executed layers."""
+    D, ff, heads, kv, E, top, eff, window = {"s": (1024, 4096, 8, 2, 32, 4, 512, 1024), "m": (2048, 8192, 16, 4, 64, 4, 1024, 2048)}[size]
+    return {"architectures": ["FlintForCausalLM"], "hidden_size": D, "num_hidden_layers": 8, "num_attention_heads": heads,
+            "num_key_value_heads": kv, "head_dim": 128, "vocab_size": 32768, "n_routed_experts": E, "num_experts_per_tok": top,
+            "moe_intermediate_size": eff, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "first_k_dense_replace": 2,
+            "intermediate_size": ff, "kv_page_size": 16, "scoring_func": "sigmoid", "sliding_window": window,
+            "sliding_window_pattern": [True] * 8}
+
+
+DESIGNS = {"pedotar": (("pedotar", pedotar_config), ("flint_dense", flint_dense_config)),
+           "kipedra": (("kipedra", kipedra_config), ("flint_routed", flint_routed_config))}
+
+
 def design_compare(args):
-    """Prefill and decode throughput of the Pedotar design beside Flint with dense feed-forwards at equal layer sizes (random
+    """Prefill and decode throughput of another design beside the closest Flint model at equal layer sizes (random
     weights), and where each model's eager steps spend their time, launcher by launcher.  One JSON line."""
     import torch
     from quench6k_b200 import ops
@@ -295,7 +324,8 @@ def design_compare(args):
            "warmup": args.warmup, "peaks": pk["source"], "sizes": {}}
     for size in [x for x in args.sizes.split(",") if x]:
         row = {}
-        for name, cfg_d in (("pedotar", pedotar_config(size)), ("flint_dense", flint_dense_config(size))):
+        for name, make in DESIGNS[args.design]:
+            cfg_d = make(size)
             arch = get_architecture(cfg_d.get("architecture") or cfg_d["architectures"][0])
             cfg = arch.config_cls.from_dict(cfg_d)
             pages = B * ((ctx + args.steps + args.warmup + 64) // page + 2) + T // page + 2
@@ -440,9 +470,10 @@ def main():
     ap.add_argument("--profile-ops", action="store_true",
                     help="instead of the benchmark line: where an eager decode step and a prefill step spend their time, launcher by "
                          "launcher (CUDA events around every launch; its own JSON line)")
-    ap.add_argument("--design", default=None, choices=["pedotar"],
-                    help="instead of the benchmark line: prefill and decode throughput of that design beside Flint with dense feed-forwards "
-                         "at equal layer sizes (--sizes), with each model's time launcher by launcher (its own JSON line)")
+    ap.add_argument("--design", default=None, choices=["pedotar", "kipedra"],
+                    help="instead of the benchmark line: prefill and decode throughput of that design beside the closest Flint model "
+                         "(pedotar: dense feed-forwards; kipedra: windows and routed experts) at equal layer sizes (--sizes), with each "
+                         "model's time launcher by launcher (its own JSON line)")
     ap.add_argument("--sizes", default="s,m", help="--design: s (width 1024) and/or m (width 2048)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill"],
                     help="time one kernel alone at the configuration's head sizes instead of the model: attention_prefill runs "

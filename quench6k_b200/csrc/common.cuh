@@ -56,6 +56,15 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
+// Activations of the products' epilogues and of the elementwise kernel, by code: 0 silu, 1 the tanh form of gelu, 2 the
+// square of relu.  An exported launcher takes the code in its epilogue argument above bit 8 (epilogue | code << 8).
+__device__ __forceinline__ float q6k_activation(float z, int act) {
+    if (act == 0) return z / (1.0f + expf(-z));
+    if (act == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    const float p = fmaxf(z, 0.0f);
+    return p * p;
+}
+
 // Programmatic dependent launch (the reference launches every Flint kernel this way,
 // crates/cuda/kernels/common.cuh:82-99).  A launch that carries the attribute may begin as soon as
 // every block of the kernel before it has executed pdl_launch() (or ended); it must execute

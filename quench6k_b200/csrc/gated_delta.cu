@@ -15,8 +15,8 @@
 //    with q and k made unit vectors per head first (q also times dk^-1/2), beta = sigmoid(b) and the decay
 //    g = exp(-exp(A_log) softplus(a + dt_bias)), all in FP32.  The columns of S do not meet: column j of S, v, u and o
 //    is a recurrence of its own given q, k, g and beta.  A block owns DELTA_COLS columns of one head of one request;
-//    DELTA_LANES lanes share a column, lane l holding rows l, l + DELTA_LANES, ...; the sums over the rows are
-//    butterflies over those lanes, so their order depends on dk alone.  Tokens of a request are walked in order, so a
+//    DELTA_LANES lanes share a column, each holding a stretch of consecutive rows; the sums over the rows are four
+//    running sums per lane and a butterfly over the lanes, so their order depends on dk alone.  Tokens of a request are walked in order, so a
 //    prompt cut anywhere leaves the same state, bit for bit, as the whole prompt.  o = S'^T q + (k . q) u uses the
 //    state after the decay, so the two sums over the rows are taken in one pass, before the write.
 //    The state is kept column-major, [slots, heads, dv, dk]: a column's rows lie together.
@@ -86,19 +86,67 @@ __global__ void __launch_bounds__(256) short_conv_tail_kernel(const float* x, in
         if (j < taps - 1) mine[(size_t)j * C + c] = keep[j];
 }
 
-// grid (heads * ceil(dv / DELTA_COLS), R), DELTA_COLS * DELTA_LANES threads.  RPL: rows of the state per lane (dk <= RPL * DELTA_LANES).
-// u: FP32 [T, ldu] with q at column 0 (G heads of dk), k after it, v after that (H heads of dv); p: FP32 [T, ldp] with
-// the H beta logits at b_col and the H decay inputs at a_col.
-template <int RPL>
-__global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(const float* u, int ldu, const float* p, int ldp, int b_col, int a_col,
-                                                                              const float* A_log, const float* dt_bias, float* state,
-                                                                              const int* q_start, const int* slot_ids, float* o, int H,
-                                                                              int G, int dk, int dv) {
+// What the recurrence needs of a token besides v, made once per token by delta_prepare_kernel for steps with long
+// portions (the recurrence kernel makes it itself for a few tokens): the unit vectors (in place over q and k in u),
+// and per token [beta (H) | decay (H) | k . q (G)] in `bg`.  The same arithmetic in the same order as the kernel below.
+__device__ __forceinline__ void delta_unit_vectors(float* ur, int q_at, int k_at, int dk, float q_mult, int lane, float* k_out, float* q_out,
+                                                   int seg, int pad, float* dot_out) {
+    float kk = 0.0f, qq = 0.0f;
+    for (int i = lane; i < dk; i += 32) {
+        const float kv = ur[k_at + i], qv = ur[q_at + i];
+        kk = fmaf(kv, kv, kk), qq = fmaf(qv, qv, qq);
+    }
+    kk = warp_sum(kk), qq = warp_sum(qq);
+    const float k_inv = rsqrtf(kk + 1e-6f), q_inv = rsqrtf(qq + 1e-6f) * q_mult;
+    float dot = 0.0f;
+    for (int i = lane; i < dk; i += 32) {
+        const float kv = ur[k_at + i] * k_inv, qv = ur[q_at + i] * q_inv;
+        const int at = seg ? (i / seg) * (seg + pad) + i % seg : i;        // seg: rows per lane of the recurrence's shared layout
+        k_out[at] = kv, q_out[at] = qv;
+        dot = fmaf(kv, qv, dot);
+    }
+    *dot_out = warp_sum(dot);
+}
+
+// grid (T), 128 threads.
+__global__ void __launch_bounds__(128) delta_prepare_kernel(float* u, int ldu, const float* p, int ldp, int b_col, int a_col, const float* A_log,
+                                                            const float* dt_bias, float* bg, int H, int G, int dk) {
     pdl_enter();
-    extern __shared__ float sm[];
-    float* s_k = sm;                                  // [TILE][dk] unit keys
-    float* s_q = s_k + DELTA_TILE * dk;               // [TILE][dk] unit queries times dk^-1/2
-    float* s_v = s_q + DELTA_TILE * dk;               // [TILE][COLS]
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* ur = u + (size_t)t * ldu;
+    float* out = bg + (size_t)t * (2 * H + G);
+    const float q_mult = rsqrtf((float)dk);
+    for (int g = warp; g < G; g += 4) {
+        float dot;
+        delta_unit_vectors(ur, g * dk, G * dk + g * dk, dk, q_mult, lane, ur + G * dk + g * dk, ur + g * dk, 0, 0, &dot);
+        if (lane == 0) out[2 * H + g] = dot;
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float* pr = p + (size_t)t * ldp;
+        out[h] = 1.0f / (1.0f + expf(-pr[b_col + h]));
+        out[H + h] = expf(-expf(A_log[h]) * softplus_f(pr[a_col + h] + dt_bias[h]));
+    }
+}
+
+// grid (heads * ceil(dv / DELTA_COLS), R), DELTA_COLS * DELTA_LANES threads.  RPL: rows of the state per lane, a multiple of 4
+// (dk <= RPL * DELTA_LANES); lane l of a column holds rows l RPL .. l RPL + RPL - 1, and in shared memory a lane's stretch
+// of k and q is RPL + 4 floats long, so that the eight lanes' 16-byte reads fall into different banks.
+// u: FP32 [T, ldu] with q at column 0 (G heads of dk), k after it, v after that (H heads of dv); p: FP32 [T, ldp] with
+// the H beta logits at b_col and the H decay inputs at a_col.  PREPARED: q and k in u are unit vectors already and bg
+// holds [beta | decay | k . q] per token (delta_prepare_kernel); the next tile's inputs are then fetched into registers
+// while this tile is walked.
+template <int RPL, bool PREPARED>
+__global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(const float* u, int ldu, const float* p, int ldp, int b_col, int a_col,
+                                                                              const float* A_log, const float* dt_bias, const float* bg,
+                                                                              float* state, const int* q_start, const int* slot_ids, float* o,
+                                                                              int H, int G, int dk, int dv) {
+    pdl_enter();
+    constexpr int SEG = RPL + 4, KS = DELTA_LANES * SEG, NT = DELTA_COLS * DELTA_LANES;
+    constexpr int PRE = PREPARED ? DELTA_TILE * DELTA_LANES * RPL / NT : 1;      // k (and q) entries of a tile per thread
+    extern __shared__ __align__(16) float sm[];
+    float* s_k = sm;                                  // [TILE][KS] unit keys
+    float* s_q = s_k + DELTA_TILE * KS;               // [TILE][KS] unit queries times dk^-1/2
+    float* s_v = s_q + DELTA_TILE * KS;               // [TILE][COLS]
     float* s_beta = s_v + DELTA_TILE * DELTA_COLS;    // [TILE]
     float* s_g = s_beta + DELTA_TILE;                 // [TILE]
     float* s_kq = s_g + DELTA_TILE;                   // [TILE]
@@ -109,74 +157,105 @@ __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(co
     const int sub = threadIdx.x % DELTA_LANES, cl = threadIdx.x / DELTA_LANES, col = col0 + cl;
     const int first = q_start[r], n = q_start[r + 1] - first;
     const int q_at = kvh * dk, k_at = G * dk + kvh * dk, v_at = 2 * G * dk + head * dv;
-    const float decay_rate = -expf(A_log[head]), bias = dt_bias[head], q_mult = rsqrtf((float)dk);
+    const float decay_rate = PREPARED ? 0.0f : -expf(A_log[head]), bias = PREPARED ? 0.0f : dt_bias[head], q_mult = rsqrtf((float)dk);
     float* mine = state + (((size_t)slot_ids[r] * H + head) * dv + (col < dv ? col : 0)) * dk;
     float S[RPL];
 #pragma unroll
     for (int i = 0; i < RPL; ++i) {
-        const int row = sub + DELTA_LANES * i;
+        const int row = sub * RPL + i;
         S[i] = col < dv && row < dk ? mine[row] : 0.0f;
     }
+    if (!PREPARED)                                    // the rows beyond dk stay zero
+        for (int i = threadIdx.x; i < 2 * DELTA_TILE * KS; i += NT) sm[i] = 0.0f;
+    float pre_k[PRE], pre_q[PRE], pre_v[DELTA_TILE * DELTA_COLS / NT], pre_s = 0.0f;
+    auto fetch = [&](int t0) {                        // PREPARED: a tile's inputs into registers
+        const int nt = min(DELTA_TILE, n - t0);
+#pragma unroll
+        for (int j = 0; j < PRE; ++j) {
+            const int idx = threadIdx.x + j * NT, t = idx / (DELTA_LANES * RPL), row = idx % (DELTA_LANES * RPL);
+            const bool ok = t < nt && row < dk;
+            const float* ur = u + (size_t)(first + t0 + t) * ldu;
+            pre_k[j] = ok ? ur[k_at + row] : 0.0f;
+            pre_q[j] = ok ? ur[q_at + row] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < DELTA_TILE * DELTA_COLS / NT; ++j) {
+            const int idx = threadIdx.x + j * NT, t = idx / DELTA_COLS, c = col0 + idx % DELTA_COLS;
+            pre_v[j] = t < nt && c < dv ? u[(size_t)(first + t0 + t) * ldu + v_at + c] : 0.0f;
+        }
+        if (threadIdx.x < 3 * DELTA_TILE) {
+            const int what = threadIdx.x / DELTA_TILE, t = threadIdx.x % DELTA_TILE;
+            const float* row = bg + (size_t)(first + t0 + t) * (2 * H + G);
+            pre_s = t < nt ? (what == 0 ? row[head] : what == 1 ? row[H + head] : row[2 * H + kvh]) : 0.0f;
+        }
+    };
+    if (PREPARED && n > 0) fetch(0);
     for (int t0 = 0; t0 < n; t0 += DELTA_TILE) {
         const int nt = min(DELTA_TILE, n - t0);
         __syncthreads();
-        // the tile's inputs: a warp per token makes the unit vectors, their product, beta and the decay
-        for (int t = warp; t < nt; t += nwarps) {
-            const float* ur = u + (size_t)(first + t0 + t) * ldu;
-            float kk = 0.0f, qq = 0.0f;
-            for (int i = lane; i < dk; i += 32) {
-                const float kv = ur[k_at + i], qv = ur[q_at + i];
-                kk = fmaf(kv, kv, kk), qq = fmaf(qv, qv, qq);
+        if (PREPARED) {
+#pragma unroll
+            for (int j = 0; j < PRE; ++j) {
+                const int idx = threadIdx.x + j * NT, t = idx / (DELTA_LANES * RPL), row = idx % (DELTA_LANES * RPL);
+                const int at = t * KS + (row / RPL) * SEG + row % RPL;
+                s_k[at] = pre_k[j], s_q[at] = pre_q[j];
             }
-            kk = warp_sum(kk), qq = warp_sum(qq);
-            const float k_inv = rsqrtf(kk + 1e-6f), q_inv = rsqrtf(qq + 1e-6f) * q_mult;
-            float dot = 0.0f;
-            for (int i = lane; i < dk; i += 32) {
-                const float kv = ur[k_at + i] * k_inv, qv = ur[q_at + i] * q_inv;
-                s_k[t * dk + i] = kv, s_q[t * dk + i] = qv;
-                dot = fmaf(kv, qv, dot);
+#pragma unroll
+            for (int j = 0; j < DELTA_TILE * DELTA_COLS / NT; ++j) s_v[threadIdx.x + j * NT] = pre_v[j];
+            if (threadIdx.x < 3 * DELTA_TILE) s_beta[threadIdx.x] = pre_s;       // s_beta, s_g and s_kq lie one after the other
+            __syncthreads();
+            if (t0 + DELTA_TILE < n) fetch(t0 + DELTA_TILE);                   // in flight while this tile is walked
+        } else {
+            // the tile's inputs: a warp per token makes the unit vectors, their product, beta and the decay
+            for (int t = warp; t < nt; t += nwarps) {
+                float dot;
+                delta_unit_vectors(const_cast<float*>(u) + (size_t)(first + t0 + t) * ldu, q_at, k_at, dk, q_mult, lane, s_k + t * KS, s_q + t * KS,
+                                   RPL, 4, &dot);
+                if (lane == 0) {
+                    const float* pr = p + (size_t)(first + t0 + t) * ldp;
+                    s_kq[t] = dot;
+                    s_beta[t] = 1.0f / (1.0f + expf(-pr[b_col + head]));
+                    s_g[t] = expf(decay_rate * softplus_f(pr[a_col + head] + bias));
+                }
             }
-            dot = warp_sum(dot);
-            if (lane == 0) {
-                const float* pr = p + (size_t)(first + t0 + t) * ldp;
-                s_kq[t] = dot;
-                s_beta[t] = 1.0f / (1.0f + expf(-pr[b_col + head]));
-                s_g[t] = expf(decay_rate * softplus_f(pr[a_col + head] + bias));
+            for (int i = threadIdx.x; i < nt * DELTA_COLS; i += NT) {
+                const int t = i / DELTA_COLS, c = col0 + i % DELTA_COLS;
+                s_v[i] = c < dv ? u[(size_t)(first + t0 + t) * ldu + v_at + c] : 0.0f;
             }
+            __syncthreads();
         }
-        for (int i = threadIdx.x; i < nt * DELTA_COLS; i += blockDim.x) {
-            const int t = i / DELTA_COLS, c = col0 + i % DELTA_COLS;
-            s_v[i] = c < dv ? u[(size_t)(first + t0 + t) * ldu + v_at + c] : 0.0f;
-        }
-        __syncthreads();
         for (int t = 0; t < nt; ++t) {
             const float g = s_g[t];
-            const float* kr = s_k + t * dk;
-            const float* qr = s_q + t * dk;
-            float kv[RPL], sk = 0.0f, sq = 0.0f;
+            const float4* kr = reinterpret_cast<const float4*>(s_k + t * KS + sub * SEG);
+            const float4* qr = reinterpret_cast<const float4*>(s_q + t * KS + sub * SEG);
+            float kv[RPL], sk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int i = 0; i < RPL; ++i) {
-                const int row = sub + DELTA_LANES * i;
-                kv[i] = row < dk ? kr[row] : 0.0f;
-                const float qv = row < dk ? qr[row] : 0.0f;
-                S[i] *= g;
-                sk = fmaf(S[i], kv[i], sk), sq = fmaf(S[i], qv, sq);
+            for (int i = 0; i < RPL / 4; ++i) {
+                const float4 k4 = kr[i], q4 = qr[i];
+                kv[4 * i] = k4.x, kv[4 * i + 1] = k4.y, kv[4 * i + 2] = k4.z, kv[4 * i + 3] = k4.w;
+                const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    S[4 * i + j] *= g;
+                    sk[j] = fmaf(S[4 * i + j], kv[4 * i + j], sk[j]), sq[j] = fmaf(S[4 * i + j], qv[j], sq[j]);
+                }
             }
+            float tk = (sk[0] + sk[1]) + (sk[2] + sk[3]), tq = (sq[0] + sq[1]) + (sq[2] + sq[3]);
 #pragma unroll
             for (int off = DELTA_LANES / 2; off > 0; off >>= 1) {
-                sk += __shfl_xor_sync(0xffffffffu, sk, off);
-                sq += __shfl_xor_sync(0xffffffffu, sq, off);
+                tk += __shfl_xor_sync(0xffffffffu, tk, off);
+                tq += __shfl_xor_sync(0xffffffffu, tq, off);
             }
-            const float uu = s_beta[t] * (s_v[t * DELTA_COLS + cl] - sk);
+            const float uu = s_beta[t] * (s_v[t * DELTA_COLS + cl] - tk);
 #pragma unroll
             for (int i = 0; i < RPL; ++i) S[i] = fmaf(kv[i], uu, S[i]);
-            if (sub == 0 && col < dv) o[(size_t)(first + t0 + t) * H * dv + head * dv + col] = fmaf(s_kq[t], uu, sq);
+            if (sub == 0 && col < dv) o[(size_t)(first + t0 + t) * H * dv + head * dv + col] = fmaf(s_kq[t], uu, tq);
         }
     }
     if (col < dv) {
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
-            const int row = sub + DELTA_LANES * i;
+            const int row = sub * RPL + i;
             if (row < dk) mine[row] = S[i];
         }
     }
@@ -227,22 +306,35 @@ Q6K_API int q6k_short_conv_tail(const float* x, int slices, long long slice_stri
 
 Q6K_API int q6k_gated_delta_max_dim() { return 32 * DELTA_LANES; }
 
-// state: FP32 [slots, H, dv, dk]; o: FP32 [T, H * dv].
-Q6K_API int q6k_gated_delta(const float* u, int ldu, const float* p, int ldp, int b_col, int a_col, const float* A_log, const float* dt_bias,
-                            float* state, const int* q_start, const int* slot_ids, float* o, int R, int H, int G, int dk, int dv,
-                            cudaStream_t st) {
-    if (R == 0) return 0;
-    Q6K_REQUIRE(R > 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, "gated_delta: bad sizes R=%d H=%d G=%d dk=%d dv=%d", R, H, G, dk, dv);
+// state: FP32 [slots, H, dv, dk]; o: FP32 [T, H * dv].  bg: null, or FP32 scratch [T, 2 H + G]: the per-token values are then made
+// by a kernel of their own first, which also turns q and k in u into unit vectors (for steps with long portions).
+Q6K_API int q6k_gated_delta(float* u, int ldu, const float* p, int ldp, int b_col, int a_col, const float* A_log, const float* dt_bias,
+                            float* bg, float* state, const int* q_start, const int* slot_ids, float* o, int T_, int R, int H, int G, int dk,
+                            int dv, cudaStream_t st) {
+    if (R == 0 || T_ == 0) return 0;
+    Q6K_REQUIRE(R > 0 && T_ > 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, "gated_delta: bad sizes R=%d H=%d G=%d dk=%d dv=%d", R, H, G, dk, dv);
     Q6K_REQUIRE(dk <= 32 * DELTA_LANES, "gated_delta: keys of %d entries exceed the supported %d", dk, 32 * DELTA_LANES);
     Q6K_REQUIRE(R <= 65535, "gated_delta: %d requests exceed the grid limit", R);
+    if (bg) {
+        q6k_launch(delta_prepare_kernel, T_, 128, 0, st, u, ldu, p, ldp, b_col, a_col, A_log, dt_bias, bg, H, G, dk);
+        if (int rc = q6k_check_launch("delta_prepare")) return rc;
+    }
     const dim3 grid(H * ((dv + DELTA_COLS - 1) / DELTA_COLS), R);
-    const size_t smem = (size_t)(2 * DELTA_TILE * dk + DELTA_TILE * DELTA_COLS + 3 * DELTA_TILE) * sizeof(float);
-    const int rpl = (dk + DELTA_LANES - 1) / DELTA_LANES;
-#define Q6K_DELTA_GO(RPL_) q6k_launch(gated_delta_kernel<RPL_>, grid, DELTA_COLS * DELTA_LANES, smem, st, u, ldu, p, ldp, b_col, a_col, A_log, dt_bias, state, q_start, slot_ids, o, H, G, dk, dv)
-    if (rpl <= 4) Q6K_DELTA_GO(4);
-    else if (rpl <= 8) Q6K_DELTA_GO(8);
-    else if (rpl <= 16) Q6K_DELTA_GO(16);
-    else Q6K_DELTA_GO(32);
+    const int rpl = ((dk + DELTA_LANES - 1) / DELTA_LANES + 3) / 4 * 4;
+    const int RPL_ = rpl <= 4 ? 4 : rpl <= 8 ? 8 : rpl <= 16 ? 16 : 32;
+    const size_t smem = (size_t)(2 * DELTA_TILE * DELTA_LANES * (RPL_ + 4) + DELTA_TILE * DELTA_COLS + 3 * DELTA_TILE) * sizeof(float);
+#define Q6K_DELTA_GO(R_, P_) q6k_launch(gated_delta_kernel<R_, P_>, grid, DELTA_COLS * DELTA_LANES, smem, st, u, ldu, p, ldp, b_col, a_col, A_log, dt_bias, bg, state, q_start, slot_ids, o, H, G, dk, dv)
+    if (bg) {
+        if (RPL_ == 4) Q6K_DELTA_GO(4, true);
+        else if (RPL_ == 8) Q6K_DELTA_GO(8, true);
+        else if (RPL_ == 16) Q6K_DELTA_GO(16, true);
+        else Q6K_DELTA_GO(32, true);
+    } else {
+        if (RPL_ == 4) Q6K_DELTA_GO(4, false);
+        else if (RPL_ == 8) Q6K_DELTA_GO(8, false);
+        else if (RPL_ == 16) Q6K_DELTA_GO(16, false);
+        else Q6K_DELTA_GO(32, false);
+    }
 #undef Q6K_DELTA_GO
     return q6k_check_launch("gated_delta");
 }

@@ -16,13 +16,13 @@ namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16;
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_ACT = 4 };      // EPI_ACT: one matrix, out = T(act(A.W))
 
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* A, int lda, const int* a_rows, const T* W, const T* W2,
                                                         size_t w_group_stride, void* out_, int ldo, int M, int N, int K,
                                                         const int* tile_group, const int* tile_row0,
-                                                        const int* group_offsets, const int* num_tiles) {
+                                                        const int* group_offsets, const int* num_tiles, int act) {
     pdl_enter();
     constexpr bool DUAL = EPI == EPI_SWIGLU;
     __shared__ float As[BK][BM + 4];
@@ -92,9 +92,11 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* A, int lda, con
                 ((float*)out_)[o] = acc[i][j];
             } else if (EPI == EPI_ADD) {
                 ((float*)out_)[o] += acc[i][j];
+            } else if (EPI == EPI_ACT) {
+                ((T*)out_)[o] = from_f32<T>(q6k_activation(acc[i][j], act));
             } else {
                 const float gte = acc[i][j];
-                ((T*)out_)[o] = from_f32<T>(gte / (1.0f + expf(-gte)) * acc2[DUAL ? i : 0][j]);
+                ((T*)out_)[o] = from_f32<T>((act == 0 ? gte / (1.0f + expf(-gte)) : q6k_activation(gte, act)) * acc2[DUAL ? i : 0][j]);
             }
         }
     }
@@ -150,7 +152,8 @@ Q6K_API int q6k_tile_list(const int* offsets, int G, int bm, int* tile_group, in
     return q6k_check_launch("tile_list");
 }
 
-// epilogue: 0 store FP32, 1 add into FP32, 2 SwiGLU of (W, W2) stored in the operand dtype.
+// epilogue: 0 store FP32, 1 add into FP32, 2 act(A.W) * (A.W2) stored in the operand dtype (SwiGLU with activation 0), 4 act(A.W)
+// stored in the operand dtype; the activation's code above bit 8.
 // Grouped when tile_group != null (max_tiles bounds the tile list; group_offsets has one more entry
 // than there are groups); otherwise one group of M rows.
 Q6K_API int q6k_gemm_simt(const void* A, int lda, const int* a_rows, const void* W, const void* W2, long long w_group_stride,
@@ -159,7 +162,9 @@ Q6K_API int q6k_gemm_simt(const void* A, int lda, const int* a_rows, const void*
                           cudaStream_t st) {
     if (M == 0 || N == 0) return 0;
     Q6K_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
-    Q6K_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm: unknown epilogue %d", epilogue);
+    const int act = epilogue >> 8;
+    epilogue &= 255;
+    Q6K_REQUIRE(((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_ACT) && act >= 0 && act <= 2, "gemm: unknown epilogue %d (activation %d)", epilogue, act);
     Q6K_REQUIRE(epilogue != EPI_SWIGLU || W2, "gemm: the SwiGLU epilogue needs two weight matrices");
     const int ytiles = tile_group ? max_tiles : (M + BM - 1) / BM;
     Q6K_REQUIRE(ytiles <= 65535, "gemm: %d row tiles exceed the grid limit", ytiles);
@@ -167,10 +172,11 @@ Q6K_API int q6k_gemm_simt(const void* A, int lda, const int* a_rows, const void*
 #define LAUNCH(EPI)                                                                                                     \
     q6k_launch(gemm_simt_kernel<T, EPI>, grid, 256, 0, st, (const T*)A, lda, a_rows, (const T*)W, (const T*)W2,                 \
                                                    (size_t)w_group_stride, out, ldo, M, N, K, tile_group, tile_row0, \
-                                                   group_offsets, num_tiles)
+                                                   group_offsets, num_tiles, act)
     Q6K_DISPATCH(dtype, {
         if (epilogue == EPI_STORE) LAUNCH(EPI_STORE);
         else if (epilogue == EPI_ADD) LAUNCH(EPI_ADD);
+        else if (epilogue == EPI_ACT) LAUNCH(EPI_ACT);
         else LAUNCH(EPI_SWIGLU);
     });
 #undef LAUNCH

@@ -37,7 +37,7 @@ constexpr int BK = 64;                 // bf16 per k-block: one 128-byte swizzle
 constexpr int WM = 128;                // weight rows per tile (UMMA M)
 constexpr int MAX_STAGES = 12;
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_ACT = 4 };   // EPI_ACT: one matrix, out = bfloat16(act(A.W))
 
 __device__ int g_tc_status = 0;
 
@@ -52,6 +52,7 @@ struct Params {
     unsigned* tickets;                 // pair mode with K slices: one arrival counter per (pair, n-tile), zero between launches
     int rows_total, N, K, ldo;
     int epilogue, stages, kb_per_split;
+    int act;                           // the activation of EPI_SWIGLU's gate and of EPI_ACT (q6k_activation's code)
     int pair_div;                      // > 0: one tile per (token, slot) pair, see q6k_gemm_tc_pairs
     int lists_old;                     // the pair list was written before the kernel launched before this one started: weights may be fetched before the wait
     int n_y, n_z;                      // row tiles (or pairs; an upper bound when num_tiles is given) and K slices
@@ -332,7 +333,8 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                         if (DUAL) b += __ldcg(mine + z * slice + p.N + n);
                     }
                     const size_t row = (size_t)tl.out0;
-                    if (p.epilogue == EPI_SWIGLU) ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(a / (1.0f + expf(-a)) * b);
+                    if (p.epilogue == EPI_SWIGLU) ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn((p.act == 0 ? a / (1.0f + expf(-a)) : q6k_activation(a, p.act)) * b);
+                    else if (p.epilogue == EPI_ACT) ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(q6k_activation(a, p.act));
                     else ((float*)p.out)[row * p.ldo + n] = a;
                 }
                 ++nt;
@@ -361,7 +363,9 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                             ((float*)p.out)[row * p.ldo + n] += v[j];
                         } else if (p.epilogue == EPI_SWIGLU) {
                             const float gte = v[j];
-                            ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(gte / (1.0f + expf(-gte)) * u[DUAL ? j : 0]);
+                            ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn((p.act == 0 ? gte / (1.0f + expf(-gte)) : q6k_activation(gte, p.act)) * u[DUAL ? j : 0]);
+                        } else if (p.epilogue == EPI_ACT) {
+                            ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(q6k_activation(v[j], p.act));
                         } else {
                             p.partial[((size_t)tl.z * p.rows_total + row) * p.N + n] = v[j];
                         }
@@ -775,7 +779,10 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     Q6K_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc: K=%d and the row pitch %lld must be multiples of 8 (TMA rows start on 16 bytes)", K, lda);
     Q6K_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && (!W2 || ((uintptr_t)W2 & 15) == 0),
                 "gemm_tc: operands must be 16-byte aligned");
-    Q6K_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tc: unknown epilogue %d", epilogue);
+    const int act = epilogue >> 8;
+    epilogue &= 255;
+    Q6K_REQUIRE(((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_ACT) && act >= 0 && act <= 2, "gemm_tc: unknown epilogue %d (activation %d)", epilogue, act);
+    Q6K_REQUIRE(epilogue != EPI_ACT || tile_group != nullptr, "gemm_tc: the activation of a single product is for grouped rows");
     const bool dual = epilogue == EPI_SWIGLU;
     Q6K_REQUIRE(!dual || W2, "gemm_tc: the SwiGLU epilogue needs two weight matrices");
     const bool grouped = tile_group != nullptr;
@@ -802,7 +809,7 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     Params p{};
     p.out = out;
     p.tile_group = tile_group, p.tile_row0 = tile_row0, p.group_offsets = group_offsets, p.num_tiles = num_tiles;
-    p.rows_total = rows_total, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue;
+    p.rows_total = rows_total, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue, p.act = act;
     // one row tile (dense), or groups of about one row tile each (experts with a prompt portion's rows): every
     // weight tile is fetched once, or by the few row tiles of its group, which lie side by side
     p.w_once = grouped ? (long long)rows_total <= 2LL * groups * bt : rows_total <= 128;
@@ -875,7 +882,9 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
     Q6K_REQUIRE(a_rows > 0 && N > 0 && K > 0 && groups > 0 && pairs > 0 && pair_div > 0, "gemm_tc_pairs: bad sizes rows=%d N=%d K=%d pairs=%d", a_rows, N, K, pairs);
     Q6K_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc_pairs: K=%d and the row pitch %lld must be multiples of 8", K, lda);
     Q6K_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && (!W2 || ((uintptr_t)W2 & 15) == 0), "gemm_tc_pairs: operands must be 16-byte aligned");
-    Q6K_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_SWIGLU, "gemm_tc_pairs: unknown epilogue %d", epilogue);
+    const int act = epilogue >> 8;
+    epilogue &= 255;
+    Q6K_REQUIRE((epilogue == EPI_STORE || epilogue == EPI_SWIGLU || epilogue == EPI_ACT) && act >= 0 && act <= 2, "gemm_tc_pairs: unknown epilogue %d (activation %d)", epilogue, act);
     const bool dual = epilogue == EPI_SWIGLU;
     Q6K_REQUIRE(!dual || W2, "gemm_tc_pairs: the SwiGLU epilogue needs two weight matrices");
     Q6K_REQUIRE((long long)groups * N < (1LL << 31), "gemm_tc_pairs: too many weight rows");
@@ -886,7 +895,7 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
         if (int rc = weight_map(&tw2, W2, (long long)groups * N, K)) return rc;
     if (int rc = make_map(&ta, A, a_rows, K, lda, 16, false)) return rc;
     Params p{};
-    p.out = out, p.tile_group = pair_expert, p.rows_total = a_rows, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue;
+    p.out = out, p.tile_group = pair_expert, p.rows_total = a_rows, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue, p.act = act;
     const int kb = (K + BK - 1) / BK;
     int splits = pair_splits(pairs, N, K);
     if (splits > 1) {

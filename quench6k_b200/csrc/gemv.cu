@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfl
                                                                long long ldo, int N, int K, int early) {
     // early: the weights (and the pair list) are older than the kernel before this one, so they may be asked for
     // before that kernel has ended (programmatic dependent launch); the activations and the output wait for it
+    const int act = early >> 8;               // the gate's activation (q6k_activation's code) rides above the flag
+    early &= 1;
     if (!early) pdl_wait();                   // an ordinary kernel: the wait first, then the signal (see common.cuh)
     pdl_launch();
     const uint64_t once = l2_evict_first_policy();
@@ -128,7 +130,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfl
         if (DUAL) s2 += meet[g * KW + q][ROWS * TT + rt];
     }
     const long long at = (orow + t) * ldo + n;
-    if (EPI == GEMV_SWIGLU) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(s / (1.0f + __expf(-s)) * s2);
+    if (EPI == GEMV_SWIGLU) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn((act == 0 ? s / (1.0f + __expf(-s)) : q6k_activation(s, act)) * s2);
     else if (EPI == GEMV_ADD) reinterpret_cast<float*>(out)[at] += s;
     else reinterpret_cast<float*>(out)[at] = s;
 }
@@ -138,7 +140,7 @@ int gemv_launch(int early, int epi, int blocks_y, cudaStream_t st, const __nv_bf
                 long long expert_stride, const int* pair_expert, int pair_div, void* out, long long ldo, int N, int K) {
     const int per_block = (GEMV_WARPS / KW) * ROWS;
     const dim3 grid((N + per_block - 1) / per_block, blocks_y);
-    const bool over = early != 0;
+    const bool over = (early & 1) != 0;
     if (epi == GEMV_SWIGLU) q6k_launch_as(over, gemv_kernel<TT, ROWS, KW, GEMV_SWIGLU>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K, early);
     else if (epi == GEMV_ADD) q6k_launch_as(over, gemv_kernel<TT, ROWS, KW, GEMV_ADD>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K, early);
     else q6k_launch_as(over, gemv_kernel<TT, ROWS, KW, GEMV_STORE>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K, early);
@@ -174,6 +176,10 @@ Q6K_API int q6k_gemv(const void* x, long long ldx, int tokens, const void* w, co
     if (tokens == 0 || (pair_expert && pairs == 0)) return 0;
     Q6K_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)w2 & 15) == 0,
                 "gemv: K=%d and the row pitch %lld must be multiples of 8 and the operands 16-byte aligned", K, ldx);
+    const int act = epi >> 8;          // the activation of the gate above bit 8
+    epi &= 255;
+    Q6K_REQUIRE(act >= 0 && act <= 2, "gemv: unknown activation %d", act);
+    early = (early ? 1 : 0) | (act << 8);
     Q6K_REQUIRE(epi >= 0 && epi <= 2 && (epi == GEMV_SWIGLU) == (w2 != nullptr), "gemv: epilogue %d with%s a second matrix", epi, w2 ? "" : "out");
     Q6K_REQUIRE(pair_expert ? (pairs > 0 && pairs <= 65535 && pair_div >= 1) : (tokens >= 1 && tokens <= q6k_gemv_max_tokens()),
                 "gemv: %d tokens (at most %d) / %d pairs", tokens, q6k_gemv_max_tokens(), pairs);

@@ -57,7 +57,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
 
 
 # kernels launched per exported function (for launch accounting in benchmarks)
-_LAUNCHES = {"q6k_attention_flex_mma": 2, "q6k_selective_scan": 1, "q6k_moe_permute": 3, "q6k_moe_plan": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
+_LAUNCHES = {"q6k_gated_delta": 1, "q6k_attention_flex_mma": 2, "q6k_selective_scan": 1, "q6k_moe_permute": 3, "q6k_moe_plan": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
 launch_count = 0
 
 
@@ -215,13 +215,31 @@ def swiglu(gu: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------- matrix products (CUDA cores)
-EPI_STORE, EPI_ADD, EPI_SWIGLU = 0, 1, 2
+EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_ACT = 0, 1, 2, 4
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+
+
+def _epilogue(w2, accumulate: bool, act: Optional[str]) -> int:
+    """The launchers' epilogue argument: with w2 the gated epilogue act(x w^T) * (x w2^T) (SwiGLU when act is None or
+    "silu"); with act alone act(x w^T), stored in the operand dtype; else store or add in FP32.  The activation's code
+    rides above bit 8."""
+    if act is not None and act not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {act!r}; known: {', '.join(ACTIVATIONS)}")
+    code = ACTIVATIONS[act] << 8 if act is not None else 0
+    if w2 is not None:
+        return EPI_SWIGLU | code
+    if act is not None:
+        if accumulate:
+            raise KernelError("an activated product is stored, not added")
+        return EPI_ACT | code
+    return EPI_ADD if accumulate else EPI_STORE
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
               w2: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None, groups=None,
-              rows: Optional[int] = None) -> torch.Tensor:
-    """out[r] (+)= a[row(r)] @ w_g^T with FP32 fused multiply-adds.
+              rows: Optional[int] = None, act: Optional[str] = None) -> torch.Tensor:
+    """out[r] (+)= a[row(r)] @ w_g^T with FP32 fused multiply-adds.  act: the gate's activation when w2 is given (default
+    silu); without w2, out = act(a w^T) in a's dtype.
 
     a: [*, K]; w: [N, K] or, grouped, [G, N, K]; w2 (same shape) switches to the SwiGLU epilogue,
     whose output has a's dtype; otherwise the output is float32.  a_rows: int32 [M] gathers rows of
@@ -237,8 +255,8 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     if grouped and groups is None:
         raise KernelError("gemm: a grouped weight needs group offsets and a tile list")
     M = rows if rows is not None else (a_rows.numel() if a_rows is not None else a.shape[0])
-    epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
-    out_dtype = a.dtype if w2 is not None else torch.float32
+    epi = _epilogue(w2, accumulate, act)
+    out_dtype = a.dtype if w2 is not None or act is not None else torch.float32
     if out is None:
         if accumulate:
             raise KernelError("gemm: accumulate needs an output")
@@ -340,7 +358,7 @@ def _workspace(nbytes: int, device, which: str = "") -> torch.Tensor:
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
             w2: Optional[torch.Tensor] = None, groups=None, bt: int = 0, rows: Optional[int] = None,
-            keep_partials: bool = False) -> torch.Tensor:
+            keep_partials: bool = False, act: Optional[str] = None) -> torch.Tensor:
     """The same contract as gemm_simt without the row gather, on tcgen05 tensor cores: bfloat16
     operands, FP32 accumulation in tensor memory.  Grouped calls pass the tile list made for
     token tile `bt` (tile_list(offsets, pairs, bt)).  keep_partials (dense, plain store): when the
@@ -358,8 +376,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     if grouped and groups is None:
         raise KernelError("gemm_tc: a grouped weight needs group offsets and a tile list")
     M = rows if rows is not None else a.shape[0]
-    epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
-    out_dtype = torch.bfloat16 if w2 is not None else torch.float32
+    epi = _epilogue(w2, accumulate, act)             # act: the gate's activation with w2; alone (grouped rows only): out = act(a w^T) in bfloat16
+    out_dtype = torch.bfloat16 if w2 is not None or act is not None else torch.float32
     lib = library()
     splits = 1
     if keep_partials:
@@ -385,7 +403,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     else:
         offsets = tile_group = tile_row0 = num_tiles = None
         max_tiles = 0
-        if w2 is None:
+        if w2 is None and act is None:
             lib.q6k_gemm_tc_workspace.restype = ctypes.c_longlong
             ws_bytes = lib.q6k_gemm_tc_workspace(_i(M), _i(N), _i(K))
             if ws_bytes:
@@ -409,7 +427,7 @@ def gemv_preferred(tokens: int, N: int, K: int) -> bool:
 
 
 def gemv(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, accumulate: bool = False,
-         pair_expert: Optional[torch.Tensor] = None, pair_div: int = 1, pairs_are_old: bool = False) -> torch.Tensor:
+         pair_expert: Optional[torch.Tensor] = None, pair_div: int = 1, pairs_are_old: bool = False, act: Optional[str] = None) -> torch.Tensor:
     """out[t] (+)= x[t] @ w^T for one to four rows of x (bfloat16, FP32 sums and output); with w2 the SwiGLU epilogue
     silu(x w^T) * (x w2^T) in bfloat16.  With pair_expert (int32 [pairs]) and w [experts, N, K]: pair y multiplies row
     y // pair_div of x with the matrix of expert pair_expert[y] and writes row y (any number of pairs).
@@ -427,7 +445,9 @@ def gemv(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, ou
         _need(pair_expert, "pair_expert", torch.int32)
         pairs = pair_expert.numel()
     rows = pairs if pair_expert is not None else x.shape[0]
-    epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
+    if act is not None and w2 is None:
+        raise KernelError("gemv: an activation goes with the gated epilogue")
+    epi = _epilogue(w2, accumulate, act)
     out_dtype = torch.bfloat16 if w2 is not None else torch.float32
     if w2 is not None:
         _need(w2, "w2", torch.bfloat16, w.shape)
@@ -462,7 +482,7 @@ def gemm_skinny_slices(tokens: int, N: int, K: int) -> int:
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                accumulate: bool = False, slices: int = 1) -> torch.Tensor:
+                accumulate: bool = False, slices: int = 1, act: Optional[str] = None) -> torch.Tensor:
     """out[t] (+)= x[t] @ w^T for at most 16 rows of x (bfloat16, FP32 sums and output) on mma.sync; with w2 the SwiGLU
     epilogue silu(x w^T) * (x w2^T) in bfloat16.  K is not split over blocks unless slices > 1 (plain products only):
     the result is then [slices, T, N] partial sums, a view of the device's scratch buffer that stays valid until the
@@ -473,7 +493,9 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = N
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm_skinny: x has K={K}, w has K={w.shape[1]}")
-    epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
+    if act is not None and w2 is None:
+        raise KernelError("gemm_skinny: an activation goes with the gated epilogue")
+    epi = _epilogue(w2, accumulate, act)
     out_dtype = torch.bfloat16 if w2 is not None else torch.float32
     if w2 is not None:
         _need(w2, "w2", torch.bfloat16, w.shape)
@@ -808,7 +830,7 @@ _pair_scratch = {}
 
 
 def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, pair_div: int, w2: Optional[torch.Tensor] = None,
-                  order: Optional[torch.Tensor] = None, pairs_are_old: bool = False) -> torch.Tensor:
+                  order: Optional[torch.Tensor] = None, pairs_are_old: bool = False, act: Optional[str] = None) -> torch.Tensor:
     """Expert products of a decode step without a permutation: pair y (= token * slots + slot)
     multiplies row y // pair_div of `a` with expert pair_expert[y]; output row y.  With w2 the
     SwiGLU epilogue (bfloat16 output), else FP32.  pairs_are_old: the caller's word that
@@ -825,7 +847,7 @@ def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, p
         raise KernelError(f"gemm_tc_pairs: a has K={a.shape[1]}, w has K={K}")
     if w2 is not None:
         _need(w2, "w2", torch.bfloat16, w.shape)
-    out = torch.empty((pairs, N), dtype=torch.bfloat16 if w2 is not None else torch.float32, device=a.device)
+    out = torch.empty((pairs, N), dtype=torch.bfloat16 if w2 is not None or act is not None else torch.float32, device=a.device)
     # a few pairs only: K is sliced over CTAs, which meet through scratch kept per device (one stream uses it at a time)
     floats, counters = ctypes.c_longlong(), ctypes.c_int()
     _call("q6k_gemm_tc_pairs_scratch", _i(pairs), _i(N), _i(K), _i(1 if w2 is not None else 0), ctypes.byref(floats), ctypes.byref(counters))
@@ -839,7 +861,7 @@ def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, p
             tickets = torch.zeros(max(counters.value, 1024), dtype=torch.int32, device=a.device)
             _pair_scratch[key] = (partial, tickets)
     _call("q6k_gemm_tc_pairs", _ptr(a), _ll(a.stride(0)), _i(a.shape[0]), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out),
-          _i(out.stride(0)), _i(EPI_SWIGLU if w2 is not None else EPI_STORE), _ptr(pair_expert), _ptr(order), _i(pairs), _i(pair_div),
+          _i(out.stride(0)), _i(_epilogue(w2, False, act)), _ptr(pair_expert), _ptr(order), _i(pairs), _i(pair_div),
           _ptr(partial), _ll(partial.numel() if partial is not None else 0), _ptr(tickets),
           _i(tickets.numel() if tickets is not None else 0), _i(1 if pairs_are_old else 0), _stream())
     return out
@@ -1252,10 +1274,13 @@ def gated_delta_max_dim() -> int:
 
 
 def gated_delta(u: torch.Tensor, p: torch.Tensor, b_col: int, a_col: int, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
-                q_start: torch.Tensor, slot_ids: torch.Tensor, R: int, H: int, G: int, dk: int, dv: int) -> torch.Tensor:
+                q_start: torch.Tensor, slot_ids: torch.Tensor, R: int, H: int, G: int, dk: int, dv: int, prepare: bool = False) -> torch.Tensor:
     """The gated delta rule over the step's rows, request by request, from and into state [slots, H, dv, dk] (FP32):
     S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with unit q (times dk^-1/2) and k.  u: FP32 [T, >= 2 G dk + H dv]
-    = [q | k | v]; p: FP32 rows holding the H beta logits at b_col and the H decay inputs at a_col.  Returns FP32 o [T, H dv]."""
+    = [q | k | v]; p: FP32 rows holding the H beta logits at b_col and the H decay inputs at a_col.  Returns FP32 o [T, H dv].
+    prepare: a kernel of its own first makes every token's unit vectors (in place over q and k in u), beta, decay and k . q,
+    and the recurrence fetches a tile of tokens while it walks the one before (for steps with long portions); else the
+    recurrence makes them itself.  The results are the same bit for bit."""
     _need(u, "u", torch.float32)
     _need(p, "p", torch.float32)
     _need(A_log, "A_log", torch.float32, (H,))
@@ -1265,8 +1290,9 @@ def gated_delta(u: torch.Tensor, p: torch.Tensor, b_col: int, a_col: int, A_log:
     if tuple(state.shape[1:]) != (H, dv, dk) or u.shape[1] < 2 * G * dk + H * dv or p.shape[0] != T or max(b_col, a_col) + H > p.shape[1]:
         raise KernelError("gated_delta: shapes disagree")
     o = torch.empty((T, H * dv), dtype=torch.float32, device=u.device)
-    _call("q6k_gated_delta", _ptr(u), _i(u.stride(0)), _ptr(p), _i(p.stride(0)), _i(b_col), _i(a_col), _ptr(A_log), _ptr(dt_bias), _ptr(state),
-          _ptr(q_start), _ptr(slot_ids), _ptr(o), _i(R), _i(H), _i(G), _i(dk), _i(dv), _stream())
+    bg = torch.empty((T, 2 * H + G), dtype=torch.float32, device=u.device) if prepare else None
+    _call("q6k_gated_delta", _ptr(u), _i(u.stride(0)), _ptr(p), _i(p.stride(0)), _i(b_col), _i(a_col), _ptr(A_log), _ptr(dt_bias), _ptr(bg),
+          _ptr(state), _ptr(q_start), _ptr(slot_ids), _ptr(o), _i(T), _i(R), _i(H), _i(G), _i(dk), _i(dv), _stream())
     return o
 
 
@@ -1326,9 +1352,6 @@ def scaled_add_norm(h: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torc
     _call("q6k_scaled_add_norm", _ptr(h), _ptr(a), _i(counts[0]), _ptr(b), _i(counts[1]), _ll(stride), _ptr(y), _ptr(pair_row), _ptr(pair_w), _i(S),
           _f(scale), _ptr(rows), _ptr(w1), _ptr(outs[0]), _ptr(w2), _ptr(outs[1]), _f(eps), _i(R), _i(D), _i(dtype_code(out_dtype)), _stream())
     return outs[0], outs[1]
-
-
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
 
 
 def activate(x: torch.Tensor, I: int, gated: bool, act: str, out_dtype: torch.dtype) -> torch.Tensor:

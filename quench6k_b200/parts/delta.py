@@ -31,6 +31,7 @@ _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "q_c
 @register_mixer("gated_delta")
 class GatedDelta(Mixer):
     graph_safe = True
+    prepare_beyond = 16          # steps whose longest portion has more tokens make the recurrence's per-token inputs in a kernel of their own
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, conv: int, eps: float, names=None):
         if num_heads % num_kv_heads:
@@ -82,7 +83,7 @@ class GatedDelta(Mixer):
         u = ops.short_conv(p, self.C, self.conv_w, None, state["conv"], ctx.req_of_token, ctx.q_start, ctx.slot_ids, ctx.R, act="silu")
         ops.current_tag = "delta.recurrence"
         o = ops.gated_delta(u, p, self.b_col, self.a_col, self.A_log, self.dt_bias, state["S"], ctx.q_start, ctx.slot_ids, ctx.R,
-                            self.H, self.G, self.dk, self.dv)
+                            self.H, self.G, self.dk, self.dv, prepare=ctx.max_q_len > self.prepare_beyond)
         ops.current_tag = "delta.out"
         y = ops.delta_out(o, p, self.g_col, self.norm_w, self.eps, self.H, self.dv, rt.dtype)
         ops.current_tag = "delta.o"

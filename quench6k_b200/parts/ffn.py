@@ -23,8 +23,7 @@ class DenseSwiGLU(FeedForward):
     graph_safe = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, names=None, act: str = "silu"):
-        """act: what the gate passes through, "silu" (the epilogue of the gate/up product) or another of ops.ACTIVATIONS
-        (then gate and up are one product and the gating a kernel of its own)."""
+        """act: what the gate passes through, one of ops.ACTIVATIONS (applied in the epilogue of the gate/up product)."""
         if act not in ops.ACTIVATIONS:
             raise ValueError(f"unknown activation {act!r}; known: {', '.join(ops.ACTIVATIONS)}")
         self.D, self.I, self.act = hidden_size, intermediate_size, act
@@ -37,22 +36,12 @@ class DenseSwiGLU(FeedForward):
 
     def bind(self, get, rt):
         self.rt = rt
-        if self.act == "silu":
-            self.w_gate, self.w_up = to_operand(get(self.names["gate"]), rt), to_operand(get(self.names["up"]), rt)
-        else:                                                       # gate and up stacked: one product yields [gate | up] per token
-            self.w_gate_up = torch.empty((2 * self.I, self.D), dtype=rt.dtype, device=rt.device)
-            self.w_gate_up[:self.I].copy_(get(self.names["gate"]))
-            self.w_gate_up[self.I:].copy_(get(self.names["up"]))
-            self.w_gate, self.w_up = self.w_gate_up[:self.I], self.w_gate_up[self.I:]
+        self.w_gate, self.w_up = to_operand(get(self.names["gate"]), rt), to_operand(get(self.names["up"]), rt)
         self.w_down = to_operand(get(self.names["down"]), rt)
 
     def _gated(self, xn):
         ops.current_tag = "dense.gate_up"
-        if self.act == "silu":
-            return linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt)
-        gu = linear.matmul(xn, self.w_gate_up, self.rt)
-        ops.current_tag = "dense.act"
-        return ops.activate(gu, self.I, True, self.act, self.rt.dtype)
+        return linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt, act=None if self.act == "silu" else self.act)
 
     def forward(self, xn, ctx, out):
         act = self._gated(xn)
@@ -82,7 +71,6 @@ class RoutedExperts(FeedForward):
         self.own_router = self.has_correction or self.route_scale != 1.0
         if self.own_router and not (scoring == "sigmoid" and renormalize):
             raise ValueError("a correction of the choice and a scale of the weights go with sigmoid scores and renormalised weights")
-        self.fused_act = self.gated and act == "silu"
         self.names = {"router": "gate.weight", "gate": "experts.gate_proj.weight", "up": "experts.up_proj.weight",
                       "down": "experts.down_proj.weight", "correction": "gate.correction", **(names or {})}
         if scoring not in ("softmax", "sigmoid"):
@@ -93,6 +81,7 @@ class RoutedExperts(FeedForward):
         self.scoring, self.renorm = scoring, bool(renormalize)
         self.shared = DenseSwiGLU(hidden_size, shared_intermediate_size) if shared_intermediate_size > 0 else None
         self.always_defers = self.shared is None      # forward(defer=True) never touches `out`
+        self.pair_tokens = 16                         # steps of at most this many tokens run the experts pair by pair
         self.routing_tap = None               # a parts.base.Tap: every forward records each row's chosen experts [T, k]
                                               # ("experts") and its router logits [T, E] ("router_logits") there
 
@@ -137,7 +126,7 @@ class RoutedExperts(FeedForward):
         T = xn.shape[0]
         pairs = T * self.k
         defer = defer and self.shared is None
-        if (self.fused_act and not self.own_router and rt.tensor_cores and not rt.is_fp32 and ops.router_small_supported(T, self.E, self.D, self.k)
+        if (self.gated and self.act == "silu" and not self.own_router and rt.tensor_cores and not rt.is_fp32 and ops.router_small_supported(T, self.E, self.D, self.k)
                 and ops.tc_supported(xn, self.w_gate) and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per
             # (token, slot) pair straight from the selection, no permutation and no gather
@@ -169,18 +158,21 @@ class RoutedExperts(FeedForward):
             sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
         if self.routing_tap is not None:
             self._tap(ctx, sel_e, logits)
+        if (T <= self.pair_tokens and defer and rt.tensor_cores and not rt.is_fp32 and ops.tc_supported(xn, self.w_up) and self.I % 8 == 0):
+            # a step of a few tokens whose router is not the one-launch kernel's: still one weight tile stream per
+            # (token, slot) pair straight from the selection, no permutation and no gather
+            ops.current_tag = "experts.gate_up"
+            act = self.act if not self.gated or self.act != "silu" else None
+            first = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up if self.gated else None, act=act)     # [pairs, I]
+            ops.current_tag = "experts.down"
+            return WeightedRows(ops.gemm_tc_pairs(first, self.w_down, sel_e, 1, pairs_are_old=True), sel_w)
         ops.current_tag = "experts.permute"
         plan = linear.group_plan(xn, self.w_gate, sel_e, rt)             # permutation by expert, row tiles, gathered rows
         ops.current_tag = "experts.gate_up"
-        if self.fused_act:
-            act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                     # [pairs, I]
+        if self.gated:
+            act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt, act=None if self.act == "silu" else self.act)   # [pairs, I]
         else:
-            first = linear.grouped_first(xn, plan, self.w_up, rt)                                 # FP32 [pairs, I]
-            if self.gated:
-                gate = linear.grouped_first(xn, plan, self.w_gate, rt)
-                first = torch.cat([gate, first], dim=1)
-            ops.current_tag = "experts.act"
-            act = ops.activate(first, self.I, self.gated, self.act, rt.dtype)
+            act = linear.grouped_activated(xn, plan, self.w_up, rt, self.act)
         ops.current_tag = "experts.down"
         y = linear.grouped_matmul(act, plan, self.w_down, rt)                                     # FP32 [pairs, D]
         if defer:

@@ -37,15 +37,15 @@ def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = N
     return ops.gemm_simt(a, w, out=out, accumulate=accumulate)
 
 
-def swiglu_matmul(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, rt) -> torch.Tensor:
-    """act[r] = silu(a[r] @ w_gate^T) * (a[r] @ w_up^T) in a's dtype."""
+def swiglu_matmul(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, rt, act=None) -> torch.Tensor:
+    """y[r] = act(a[r] @ w_gate^T) * (a[r] @ w_up^T) in a's dtype; act None: silu."""
     if _tc(a, w_gate, rt):
         if ops.gemv_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
-            return ops.gemv(a, w_gate, w2=w_up)
+            return ops.gemv(a, w_gate, w2=w_up, act=act)
         if ops.gemm_skinny_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
-            return ops.gemm_skinny(a, w_gate, w2=w_up)
-        return ops.gemm_tc(a, w_gate, w2=w_up)
-    return ops.gemm_simt(a, w_gate, w2=w_up)
+            return ops.gemm_skinny(a, w_gate, w2=w_up, act=act)
+        return ops.gemm_tc(a, w_gate, w2=w_up, act=act)
+    return ops.gemm_simt(a, w_gate, w2=w_up, act=act)
 
 
 class GroupPlan:
@@ -74,19 +74,19 @@ def group_plan(a: torch.Tensor, w: torch.Tensor, sel_e: torch.Tensor, rt) -> Gro
     return GroupPlan(a, sel_e, w.shape[0], rt, _tc(a, w, rt) and a.is_contiguous())
 
 
-def grouped_swiglu(a: torch.Tensor, plan: GroupPlan, w_gate: torch.Tensor, w_up: torch.Tensor, rt) -> torch.Tensor:
-    """act[row] = SwiGLU of a[row_token[row]] with the weights of the row's group; [pairs, I]."""
+def grouped_swiglu(a: torch.Tensor, plan: GroupPlan, w_gate: torch.Tensor, w_up: torch.Tensor, rt, act=None) -> torch.Tensor:
+    """y[row] = act(x w_gate^T) * (x w_up^T) for x = a[row_token[row]] with the weights of the row's group (act None: silu); [pairs, I]."""
     if plan.tc:
-        return ops.gemm_tc(plan.xs, w_gate, w2=w_up, groups=plan.tiles, bt=plan.bt, rows=plan.pairs)
-    return ops.gemm_simt(a, w_gate, w2=w_up, a_rows=plan.row_token, groups=plan.tiles, rows=plan.pairs)
+        return ops.gemm_tc(plan.xs, w_gate, w2=w_up, groups=plan.tiles, bt=plan.bt, rows=plan.pairs, act=act)
+    return ops.gemm_simt(a, w_gate, w2=w_up, a_rows=plan.row_token, groups=plan.tiles, rows=plan.pairs, act=act)
 
 
-def grouped_first(a: torch.Tensor, plan: GroupPlan, w: torch.Tensor, rt) -> torch.Tensor:
-    """FP32 y[row] = a[row_token[row]] @ w_g^T with the weights of the row's group: the experts' first product without an
-    activation in its epilogue; [pairs, N]."""
+def grouped_activated(a: torch.Tensor, plan: GroupPlan, w: torch.Tensor, rt, act: str) -> torch.Tensor:
+    """y[row] = act(a[row_token[row]] @ w_g^T) in a's dtype with the weights of the row's group: the first product of
+    experts that have no gate; [pairs, N]."""
     if plan.tc:
-        return ops.gemm_tc(plan.xs, w, groups=plan.tiles, bt=plan.bt, rows=plan.pairs)
-    return ops.gemm_simt(a, w, a_rows=plan.row_token, groups=plan.tiles, rows=plan.pairs)
+        return ops.gemm_tc(plan.xs, w, groups=plan.tiles, bt=plan.bt, rows=plan.pairs, act=act)
+    return ops.gemm_simt(a, w, a_rows=plan.row_token, groups=plan.tiles, rows=plan.pairs, act=act)
 
 
 def grouped_matmul(a: torch.Tensor, plan: GroupPlan, w: torch.Tensor, rt) -> torch.Tensor:

@@ -80,20 +80,21 @@ def test_gated_delta_kernel_in_portions(H, G, dk, dv):
             S = S + torch.outer(k[t, h // (H // G)], beta[t, h] * (v[t, h] - S.T @ k[t, h // (H // G)]))
             want[t, h] = S.T @ q[t, h // (H // G)]
     results = []
-    for cuts in ([n], [1, 2, 30, 1, 17, 24]):
+    for cuts, prepare in (([n], False), ([1, 2, 30, 1, 17, 24], False), ([n], True), ([40, 3, 32], True)):
         state = torch.zeros(3, H, dv, dk).cuda()
         outs, at = [], 0
         for c in cuts:
             ctx = helpers.make_context([c], [at], [[[0]]])
             ctx.slot_ids = torch.tensor([2], dtype=torch.int32).cuda()
             outs.append(ops.gated_delta(u[at:at + c].contiguous().cuda(), p[at:at + c].contiguous().cuda(), 1, 2 + H, A_log.cuda(), dt_bias.cuda(),
-                                        state, ctx.q_start, ctx.slot_ids, 1, H, G, dk, dv))
+                                        state, ctx.q_start, ctx.slot_ids, 1, H, G, dk, dv, prepare=prepare))
             at += c
         results.append((torch.cat(outs).cpu(), state.cpu()))
         err = (results[-1][0].double().view(n, H, dv) - want).abs().max() / want.abs().max()
         assert err < 2e-5, f"cuts {cuts}: {float(err):.3e}"
         assert bool((state[:2] == 0).all())
-    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    for other in results[1:]:
+        assert torch.equal(results[0][0], other[0]) and torch.equal(results[0][1], other[1])
 
 
 @pytest.mark.parametrize("D", [50, 256, 1000])
