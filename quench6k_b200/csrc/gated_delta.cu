@@ -17,8 +17,8 @@
 //    is a recurrence of its own given q, k, g and beta.  A block owns DELTA_COLS columns of one head of one request;
 //    DELTA_LANES lanes share a column, each holding a stretch of consecutive rows; the sums over the rows are four
 //    running sums per lane and a butterfly over the lanes, so their order depends on dk alone.  Tokens of a request are walked in order, so a
-//    prompt cut anywhere leaves the same state, bit for bit, as the whole prompt.  o = S'^T q + (k . q) u uses the
-//    state after the decay, so the two sums over the rows are taken in one pass, before the write.
+//    prompt cut anywhere leaves the same state as the whole prompt (up to rounding: tokens are taken a few at a time,
+//    counted from the start of a portion, see gated_delta_kernel).
 //    The state is kept column-major, [slots, heads, dv, dk]: a column's rows lie together.
 //
 //    delta_out_kernel closes the mixer: every head's o is divided by its root mean square over dv, multiplied by a
@@ -88,9 +88,9 @@ __global__ void __launch_bounds__(256) short_conv_tail_kernel(const float* x, in
 
 // What the recurrence needs of a token besides v, made once per token by delta_prepare_kernel for steps with long
 // portions (the recurrence kernel makes it itself for a few tokens): the unit vectors (in place over q and k in u),
-// and per token [beta (H) | decay (H) | k . q (G)] in `bg`.  The same arithmetic in the same order as the kernel below.
+// and per token [beta (H) | decay (H)] in `bg`.  The same arithmetic in the same order as in the kernel below.
 __device__ __forceinline__ void delta_unit_vectors(float* ur, int q_at, int k_at, int dk, float q_mult, int lane, float* k_out, float* q_out,
-                                                   int seg, int pad, float* dot_out) {
+                                                   int seg, int pad) {
     float kk = 0.0f, qq = 0.0f;
     for (int i = lane; i < dk; i += 32) {
         const float kv = ur[k_at + i], qv = ur[q_at + i];
@@ -98,14 +98,11 @@ __device__ __forceinline__ void delta_unit_vectors(float* ur, int q_at, int k_at
     }
     kk = warp_sum(kk), qq = warp_sum(qq);
     const float k_inv = rsqrtf(kk + 1e-6f), q_inv = rsqrtf(qq + 1e-6f) * q_mult;
-    float dot = 0.0f;
     for (int i = lane; i < dk; i += 32) {
         const float kv = ur[k_at + i] * k_inv, qv = ur[q_at + i] * q_inv;
         const int at = seg ? (i / seg) * (seg + pad) + i % seg : i;        // seg: rows per lane of the recurrence's shared layout
         k_out[at] = kv, q_out[at] = qv;
-        dot = fmaf(kv, qv, dot);
     }
-    *dot_out = warp_sum(dot);
 }
 
 // grid (T), 128 threads.
@@ -114,13 +111,9 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(float* u, int ldu, c
     pdl_enter();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* ur = u + (size_t)t * ldu;
-    float* out = bg + (size_t)t * (2 * H + G);
+    float* out = bg + (size_t)t * 2 * H;
     const float q_mult = rsqrtf((float)dk);
-    for (int g = warp; g < G; g += 4) {
-        float dot;
-        delta_unit_vectors(ur, g * dk, G * dk + g * dk, dk, q_mult, lane, ur + G * dk + g * dk, ur + g * dk, 0, 0, &dot);
-        if (lane == 0) out[2 * H + g] = dot;
-    }
+    for (int g = warp; g < G; g += 4) delta_unit_vectors(ur, g * dk, G * dk + g * dk, dk, q_mult, lane, ur + G * dk + g * dk, ur + g * dk, 0, 0);
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         const float* pr = p + (size_t)t * ldp;
         out[h] = 1.0f / (1.0f + expf(-pr[b_col + h]));
@@ -131,25 +124,38 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(float* u, int ldu, c
 // grid (heads * ceil(dv / DELTA_COLS), R), DELTA_COLS * DELTA_LANES threads.  RPL: rows of the state per lane, a multiple of 4
 // (dk <= RPL * DELTA_LANES); lane l of a column holds rows l RPL .. l RPL + RPL - 1, and in shared memory a lane's stretch
 // of k and q is RPL + 4 floats long, so that the eight lanes' 16-byte reads fall into different banks.
+//
+// Tokens are taken DELTA_CHUNK at a time, counted from the start of the request's portion.  With S the state before the
+// chunk, P_i the product of the decays up to token i, and w_m = u_m times the decays after token m up to the one at hand,
+//   S_(i-1)^T k_i = P_(i-1) (S^T k_i) + sum_(m<i) w_m (k_m . k_i),      likewise with q_i,
+// so one pass over S gives the sums with every k_i and q_i of the chunk (one butterfly over the lanes for all of them),
+// a few scalar steps per column give u_i and o_i in order, and one more pass writes S <- P S + sum_m w_m k_m.  The
+// products k_m . k_i and k_m . q_i of a chunk do not depend on the column; a warp makes them when the tile is staged.
+// Against the walk token by token this only regroups sums: results differ by rounding, also between two ways to cut a prompt.
+//
 // u: FP32 [T, ldu] with q at column 0 (G heads of dk), k after it, v after that (H heads of dv); p: FP32 [T, ldp] with
 // the H beta logits at b_col and the H decay inputs at a_col.  PREPARED: q and k in u are unit vectors already and bg
-// holds [beta | decay | k . q] per token (delta_prepare_kernel); the next tile's inputs are then fetched into registers
-// while this tile is walked.
+// holds [beta | decay] per token (delta_prepare_kernel); the next tile's inputs are then fetched into registers while
+// this tile is walked.
+constexpr int DELTA_CHUNK = 4;
+
 template <int RPL, bool PREPARED>
 __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(const float* u, int ldu, const float* p, int ldp, int b_col, int a_col,
                                                                               const float* A_log, const float* dt_bias, const float* bg,
                                                                               float* state, const int* q_start, const int* slot_ids, float* o,
                                                                               int H, int G, int dk, int dv) {
     pdl_enter();
-    constexpr int SEG = RPL + 4, KS = DELTA_LANES * SEG, NT = DELTA_COLS * DELTA_LANES;
+    constexpr int SEG = RPL + 4, KS = DELTA_LANES * SEG, NT = DELTA_COLS * DELTA_LANES, CH = DELTA_CHUNK;
     constexpr int PRE = PREPARED ? DELTA_TILE * DELTA_LANES * RPL / NT : 1;      // k (and q) entries of a tile per thread
+    static_assert(DELTA_TILE % CH == 0 && DELTA_TILE / CH == NT / 32, "one warp per chunk of a tile");
     extern __shared__ __align__(16) float sm[];
     float* s_k = sm;                                  // [TILE][KS] unit keys
     float* s_q = s_k + DELTA_TILE * KS;               // [TILE][KS] unit queries times dk^-1/2
     float* s_v = s_q + DELTA_TILE * KS;               // [TILE][COLS]
     float* s_beta = s_v + DELTA_TILE * DELTA_COLS;    // [TILE]
     float* s_g = s_beta + DELTA_TILE;                 // [TILE]
-    float* s_kq = s_g + DELTA_TILE;                   // [TILE]
+    float* s_kk = s_g + DELTA_TILE;                   // [TILE][CH]: k_m . k_i for token m and place i of its chunk (m's place < i)
+    float* s_kq = s_kk + DELTA_TILE * CH;             // [TILE][CH]: k_m . q_i (m's place <= i)
     const int col_blocks = (dv + DELTA_COLS - 1) / DELTA_COLS;
     const int head = blockIdx.x / col_blocks, col0 = (blockIdx.x % col_blocks) * DELTA_COLS, r = blockIdx.y;
     const int kvh = head / (H / G);
@@ -165,8 +171,9 @@ __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(co
         const int row = sub * RPL + i;
         S[i] = col < dv && row < dk ? mine[row] : 0.0f;
     }
-    if (!PREPARED)                                    // the rows beyond dk stay zero
-        for (int i = threadIdx.x; i < 2 * DELTA_TILE * KS; i += NT) sm[i] = 0.0f;
+    // the padding of the stretches, the rows beyond dk and the tokens beyond a portion read as zero (the products within a
+    // chunk are summed over whole stretches)
+    for (int i = threadIdx.x; i < 2 * DELTA_TILE * KS; i += NT) sm[i] = 0.0f;
     float pre_k[PRE], pre_q[PRE], pre_v[DELTA_TILE * DELTA_COLS / NT], pre_s = 0.0f;
     auto fetch = [&](int t0) {                        // PREPARED: a tile's inputs into registers
         const int nt = min(DELTA_TILE, n - t0);
@@ -183,10 +190,9 @@ __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(co
             const int idx = threadIdx.x + j * NT, t = idx / DELTA_COLS, c = col0 + idx % DELTA_COLS;
             pre_v[j] = t < nt && c < dv ? u[(size_t)(first + t0 + t) * ldu + v_at + c] : 0.0f;
         }
-        if (threadIdx.x < 3 * DELTA_TILE) {
+        if (threadIdx.x < 2 * DELTA_TILE) {
             const int what = threadIdx.x / DELTA_TILE, t = threadIdx.x % DELTA_TILE;
-            const float* row = bg + (size_t)(first + t0 + t) * (2 * H + G);
-            pre_s = t < nt ? (what == 0 ? row[head] : what == 1 ? row[H + head] : row[2 * H + kvh]) : 0.0f;
+            pre_s = t < nt ? bg[(size_t)(first + t0 + t) * 2 * H + what * H + head] : 0.0f;
         }
     };
     if (PREPARED && n > 0) fetch(0);
@@ -202,18 +208,16 @@ __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(co
             }
 #pragma unroll
             for (int j = 0; j < DELTA_TILE * DELTA_COLS / NT; ++j) s_v[threadIdx.x + j * NT] = pre_v[j];
-            if (threadIdx.x < 3 * DELTA_TILE) s_beta[threadIdx.x] = pre_s;       // s_beta, s_g and s_kq lie one after the other
+            if (threadIdx.x < 2 * DELTA_TILE) s_beta[threadIdx.x] = pre_s;       // s_beta and s_g lie one after the other
             __syncthreads();
             if (t0 + DELTA_TILE < n) fetch(t0 + DELTA_TILE);                   // in flight while this tile is walked
         } else {
-            // the tile's inputs: a warp per token makes the unit vectors, their product, beta and the decay
+            // the tile's inputs: a warp per token makes the unit vectors, beta and the decay
             for (int t = warp; t < nt; t += nwarps) {
-                float dot;
                 delta_unit_vectors(const_cast<float*>(u) + (size_t)(first + t0 + t) * ldu, q_at, k_at, dk, q_mult, lane, s_k + t * KS, s_q + t * KS,
-                                   RPL, 4, &dot);
+                                   RPL, 4);
                 if (lane == 0) {
                     const float* pr = p + (size_t)(first + t0 + t) * ldp;
-                    s_kq[t] = dot;
                     s_beta[t] = 1.0f / (1.0f + expf(-pr[b_col + head]));
                     s_g[t] = expf(decay_rate * softplus_f(pr[a_col + head] + bias));
                 }
@@ -224,32 +228,91 @@ __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(co
             }
             __syncthreads();
         }
-        for (int t = 0; t < nt; ++t) {
-            const float g = s_g[t];
-            const float4* kr = reinterpret_cast<const float4*>(s_k + t * KS + sub * SEG);
-            const float4* qr = reinterpret_cast<const float4*>(s_q + t * KS + sub * SEG);
-            float kv[RPL], sk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // the products within each chunk: warp c makes those of chunk c (sums over the padded stretches, whose padding is zero)
+        if (warp * CH < nt) {
+            float kk[CH][CH], kq[CH][CH];
+#pragma unroll
+            for (int m = 0; m < CH; ++m)
+#pragma unroll
+                for (int i = 0; i < CH; ++i) kk[m][i] = 0.0f, kq[m][i] = 0.0f;
+            const float* kb = s_k + warp * CH * KS;
+            const float* qb = s_q + warp * CH * KS;
+            for (int x = lane; x < KS; x += 32) {
+                float kx[CH], qx[CH];
+#pragma unroll
+                for (int m = 0; m < CH; ++m) kx[m] = kb[m * KS + x], qx[m] = qb[m * KS + x];
+#pragma unroll
+                for (int m = 0; m < CH; ++m)
+#pragma unroll
+                    for (int i = m; i < CH; ++i) {
+                        kq[m][i] = fmaf(kx[m], qx[i], kq[m][i]);
+                        if (i > m) kk[m][i] = fmaf(kx[m], kx[i], kk[m][i]);
+                    }
+            }
+#pragma unroll
+            for (int m = 0; m < CH; ++m)
+#pragma unroll
+                for (int i = m; i < CH; ++i) {
+                    const float a = warp_sum(kq[m][i]);
+                    const float b = i > m ? warp_sum(kk[m][i]) : 0.0f;
+                    if (lane == 0) s_kq[(warp * CH + m) * CH + i] = a, s_kk[(warp * CH + m) * CH + i] = b;
+                }
+        }
+        __syncthreads();
+        for (int c0 = 0; c0 < nt; c0 += CH) {
+            const int cnt = min(CH, nt - c0);
+            float sk[CH], sq[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) sk[c] = 0.0f, sq[c] = 0.0f;
 #pragma unroll
             for (int i = 0; i < RPL / 4; ++i) {
-                const float4 k4 = kr[i], q4 = qr[i];
-                kv[4 * i] = k4.x, kv[4 * i + 1] = k4.y, kv[4 * i + 2] = k4.z, kv[4 * i + 3] = k4.w;
-                const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    S[4 * i + j] *= g;
-                    sk[j] = fmaf(S[4 * i + j], kv[4 * i + j], sk[j]), sq[j] = fmaf(S[4 * i + j], qv[j], sq[j]);
+                for (int c = 0; c < CH; ++c) {
+                    const float4 k4 = reinterpret_cast<const float4*>(s_k + (c0 + c) * KS + sub * SEG)[i];
+                    const float4 q4 = reinterpret_cast<const float4*>(s_q + (c0 + c) * KS + sub * SEG)[i];
+                    sk[c] = fmaf(S[4 * i], k4.x, sk[c]), sk[c] = fmaf(S[4 * i + 1], k4.y, sk[c]);
+                    sk[c] = fmaf(S[4 * i + 2], k4.z, sk[c]), sk[c] = fmaf(S[4 * i + 3], k4.w, sk[c]);
+                    sq[c] = fmaf(S[4 * i], q4.x, sq[c]), sq[c] = fmaf(S[4 * i + 1], q4.y, sq[c]);
+                    sq[c] = fmaf(S[4 * i + 2], q4.z, sq[c]), sq[c] = fmaf(S[4 * i + 3], q4.w, sq[c]);
                 }
             }
-            float tk = (sk[0] + sk[1]) + (sk[2] + sk[3]), tq = (sq[0] + sq[1]) + (sq[2] + sq[3]);
 #pragma unroll
             for (int off = DELTA_LANES / 2; off > 0; off >>= 1) {
-                tk += __shfl_xor_sync(0xffffffffu, tk, off);
-                tq += __shfl_xor_sync(0xffffffffu, tq, off);
-            }
-            const float uu = s_beta[t] * (s_v[t * DELTA_COLS + cl] - tk);
 #pragma unroll
-            for (int i = 0; i < RPL; ++i) S[i] = fmaf(kv[i], uu, S[i]);
-            if (sub == 0 && col < dv) o[(size_t)(first + t0 + t) * H * dv + head * dv + col] = fmaf(s_kq[t], uu, tq);
+                for (int c = 0; c < CH; ++c) {
+                    sk[c] += __shfl_xor_sync(0xffffffffu, sk[c], off);
+                    sq[c] += __shfl_xor_sync(0xffffffffu, sq[c], off);
+                }
+            }
+            float P = 1.0f, w[CH];
+#pragma unroll
+            for (int i = 0; i < CH; ++i) {
+                const bool live = i < cnt;
+                const float g = live ? s_g[c0 + i] : 1.0f;
+                float a = P * sk[i], b = P * sq[i];
+#pragma unroll
+                for (int m = 0; m < i; ++m) {
+                    a = fmaf(w[m], s_kk[(c0 + m) * CH + i], a);
+                    b = fmaf(w[m], s_kq[(c0 + m) * CH + i], b);
+                }
+                const float uu = live ? s_beta[c0 + i] * (s_v[(c0 + i) * DELTA_COLS + cl] - g * a) : 0.0f;
+                if (live && sub == 0 && col < dv) o[(size_t)(first + t0 + c0 + i) * H * dv + head * dv + col] = fmaf(s_kq[(c0 + i) * CH + i], uu, g * b);
+                P *= g;
+#pragma unroll
+                for (int m = 0; m < i; ++m) w[m] *= g;
+                w[i] = uu;
+            }
+#pragma unroll
+            for (int i = 0; i < RPL / 4; ++i) {
+                float acc[4] = {P * S[4 * i], P * S[4 * i + 1], P * S[4 * i + 2], P * S[4 * i + 3]};
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    const float4 k4 = reinterpret_cast<const float4*>(s_k + (c0 + c) * KS + sub * SEG)[i];
+                    acc[0] = fmaf(w[c], k4.x, acc[0]), acc[1] = fmaf(w[c], k4.y, acc[1]);
+                    acc[2] = fmaf(w[c], k4.z, acc[2]), acc[3] = fmaf(w[c], k4.w, acc[3]);
+                }
+                S[4 * i] = acc[0], S[4 * i + 1] = acc[1], S[4 * i + 2] = acc[2], S[4 * i + 3] = acc[3];
+            }
         }
     }
     if (col < dv) {
@@ -306,7 +369,7 @@ Q6K_API int q6k_short_conv_tail(const float* x, int slices, long long slice_stri
 
 Q6K_API int q6k_gated_delta_max_dim() { return 32 * DELTA_LANES; }
 
-// state: FP32 [slots, H, dv, dk]; o: FP32 [T, H * dv].  bg: null, or FP32 scratch [T, 2 H + G]: the per-token values are then made
+// state: FP32 [slots, H, dv, dk]; o: FP32 [T, H * dv].  bg: null, or FP32 scratch [T, 2 H]: the per-token values are then made
 // by a kernel of their own first, which also turns q and k in u into unit vectors (for steps with long portions).
 Q6K_API int q6k_gated_delta(float* u, int ldu, const float* p, int ldp, int b_col, int a_col, const float* A_log, const float* dt_bias,
                             float* bg, float* state, const int* q_start, const int* slot_ids, float* o, int T_, int R, int H, int G, int dk,
@@ -322,7 +385,7 @@ Q6K_API int q6k_gated_delta(float* u, int ldu, const float* p, int ldp, int b_co
     const dim3 grid(H * ((dv + DELTA_COLS - 1) / DELTA_COLS), R);
     const int rpl = ((dk + DELTA_LANES - 1) / DELTA_LANES + 3) / 4 * 4;
     const int RPL_ = rpl <= 4 ? 4 : rpl <= 8 ? 8 : rpl <= 16 ? 16 : 32;
-    const size_t smem = (size_t)(2 * DELTA_TILE * DELTA_LANES * (RPL_ + 4) + DELTA_TILE * DELTA_COLS + 3 * DELTA_TILE) * sizeof(float);
+    const size_t smem = (size_t)(2 * DELTA_TILE * DELTA_LANES * (RPL_ + 4) + DELTA_TILE * DELTA_COLS + 2 * DELTA_TILE + 2 * DELTA_TILE * DELTA_CHUNK) * sizeof(float);
 #define Q6K_DELTA_GO(R_, P_) q6k_launch(gated_delta_kernel<R_, P_>, grid, DELTA_COLS * DELTA_LANES, smem, st, u, ldu, p, ldp, b_col, a_col, A_log, dt_bias, bg, state, q_start, slot_ids, o, H, G, dk, dv)
     if (bg) {
         if (RPL_ == 4) Q6K_DELTA_GO(4, true);

@@ -56,8 +56,9 @@ def test_short_convolution_with_tails(C, taps, act):
 
 @pytest.mark.parametrize("H, G, dk, dv", [(4, 2, 24, 12), (3, 3, 100, 20), (2, 1, 136, 33), (5, 5, 7, 9), (2, 2, 256, 16)])
 def test_gated_delta_kernel_in_portions(H, G, dk, dv):
-    """The recurrence over two requests, one cut into portions of changing size, against loops in double precision; the
-    state of each request lives in its slot from step to step, bit for bit the same however the prompt is cut."""
+    """The recurrence over a request, whole and cut into portions of changing size, with the per-token inputs made inside
+    the kernel and by the kernel of their own, against loops in double precision; the state lives in the request's slot
+    from step to step and is the same, up to FP32 rounding, however the prompt is cut."""
     from quench6k_b200 import ops
     g = torch.Generator().manual_seed(H * dk + dv)
     n, C = 75, 2 * G * dk + H * dv
@@ -80,7 +81,7 @@ def test_gated_delta_kernel_in_portions(H, G, dk, dv):
             S = S + torch.outer(k[t, h // (H // G)], beta[t, h] * (v[t, h] - S.T @ k[t, h // (H // G)]))
             want[t, h] = S.T @ q[t, h // (H // G)]
     results = []
-    for cuts, prepare in (([n], False), ([1, 2, 30, 1, 17, 24], False), ([n], True), ([40, 3, 32], True)):
+    for cuts, prepare in (([n], True), ([n], False), ([1, 2, 30, 1, 17, 24], False), ([40, 3, 32], True)):
         state = torch.zeros(3, H, dv, dk).cuda()
         outs, at = [], 0
         for c in cuts:
@@ -94,7 +95,8 @@ def test_gated_delta_kernel_in_portions(H, G, dk, dv):
         assert err < 2e-5, f"cuts {cuts}: {float(err):.3e}"
         assert bool((state[:2] == 0).all())
     for other in results[1:]:
-        assert torch.equal(results[0][0], other[0]) and torch.equal(results[0][1], other[1])
+        for a, b in zip(results[0], other):
+            assert float((a - b).abs().max()) <= 2e-6 * float(a.abs().max())
 
 
 @pytest.mark.parametrize("D", [50, 256, 1000])
