@@ -217,6 +217,41 @@ def kernel_attention_prefill(args):
     return 0
 
 
+def kernel_gated_delta(args):
+    """The gated delta rule recurrence alone (with the kernel that prepares its per-token inputs): one request's portion of
+    --prefill-tokens tokens, 16 heads of 128 x 128 on 4 key heads, or --batch requests of one token each (a decode step);
+    CUDA events after warm-up.  Counted: 3 passes of 2 dk dv FLOPs per token and head (two sums over the state, one write)."""
+    import torch
+    from quench6k_b200 import ops
+    H, G, dk, dv, dev = 16, 4, 128, 128, "cuda:0"
+    decode = bool(args.batch)
+    R, n = (args.batch, 1) if decode else (1, args.prefill_tokens)
+    T = R * n
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    u = torch.randn(T, 2 * G * dk + H * dv, device=dev)
+    p = torch.randn(T, 2 * H, device=dev)
+    A_log, dt_bias = torch.randn(H, device=dev) - 3.0, torch.randn(H, device=dev)
+    state = torch.zeros(R, H, dv, dk, device=dev)
+    q_start, slots = i32([i * n for i in range(R + 1)]), i32(list(range(R)))
+    run = lambda: ops.gated_delta(u.clone() if not decode else u, p, 0, H, A_log, dt_bias, state, q_start, slots, R, H, G, dk, dv, prepare=n > 16)
+    for _ in range(max(3, args.warmup)):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 6.0 * dk * dv * H * T
+    state_bytes = 2.0 * 4 * H * dk * dv * R
+    print(json.dumps({"kernel": "gated_delta", "requests": R, "tokens_each": n, "us": round(ms * 1e3, 1), "ns_per_token": round(ms * 1e6 / n, 1),
+                      "gflops": round(flops / ms / 1e6, 1), "state_gbs": round(state_bytes / ms / 1e6, 1), "steps": args.steps,
+                      "note": "prompt portions include a device copy of the inputs (the kernel normalises q and k in place)"}))
+    return 0
+
+
 def profile_ops(args, runner, cfg_d, layers, ctx, stand_at_context, rand_ids):
     """Where the time of an eager decode step (batch --batch at the context) and of a prefill step goes, launcher by
     launcher: CUDA events around every launch (quench6k_b200.ops.profile_begin/profile_end), no profiler involved.  Eager
@@ -475,9 +510,10 @@ def main():
                          "(pedotar: dense feed-forwards; kipedra: windows and routed experts) at equal layer sizes (--sizes), with each "
                          "model's time launcher by launcher (its own JSON line)")
     ap.add_argument("--sizes", default="s,m", help="--design: s (width 1024) and/or m (width 2048)")
-    ap.add_argument("--kernel", default=None, choices=["attention_prefill"],
+    ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gated_delta"],
                     help="time one kernel alone at the configuration's head sizes instead of the model: attention_prefill runs "
-                         "--prefill-tokens query tokens that end at position --context (one request, contiguous pages)")
+                         "--prefill-tokens query tokens that end at position --context (one request, contiguous pages); gated_delta runs "
+                         "the delta rule recurrence over one portion of --prefill-tokens tokens, or with --batch over that many single tokens")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -498,6 +534,8 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     if args.kernel == "attention_prefill":
         return kernel_attention_prefill(args)
+    if args.kernel == "gated_delta":
+        return kernel_gated_delta(args)
     if args.design:
         torch.cuda.set_device(0)
         return design_compare(args)

@@ -15,8 +15,8 @@
 //    with q and k made unit vectors per head first (q also times dk^-1/2), beta = sigmoid(b) and the decay
 //    g = exp(-exp(A_log) softplus(a + dt_bias)), all in FP32.  The columns of S do not meet: column j of S, v, u and o
 //    is a recurrence of its own given q, k, g and beta.  A block owns DELTA_COLS columns of one head of one request;
-//    DELTA_LANES lanes share a column, each holding a stretch of consecutive rows; the sums over the rows are four
-//    running sums per lane and a butterfly over the lanes, so their order depends on dk alone.  Tokens of a request are walked in order, so a
+//    DELTA_LANES lanes share a column, each holding a stretch of consecutive rows; the sums over the rows are a running
+//    sum per lane and a butterfly over the lanes, so their order depends on dk alone.
 //    prompt cut anywhere leaves the same state as the whole prompt (up to rounding: tokens are taken a few at a time,
 //    counted from the start of a portion, see gated_delta_kernel).
 //    The state is kept column-major, [slots, heads, dv, dk]: a column's rows lie together.
@@ -28,8 +28,10 @@
 namespace {
 
 constexpr int CONV_MAX_TAPS = 16;
-constexpr int DELTA_LANES = 8;
-constexpr int DELTA_COLS = 16;
+constexpr int DELTA_LANES = 8;       // lanes that share a column of the state
+constexpr int DELTA_COLS = 16;      // columns of the state per block
+constexpr int DELTA_PER = 1;        // of them per thread (what a thread reads of k and q serves all of its columns)
+constexpr int DELTA_THREADS = DELTA_COLS / DELTA_PER * DELTA_LANES;
 constexpr int DELTA_TILE = 16;       // tokens whose inputs are staged in shared memory at a time
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
@@ -121,9 +123,9 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(float* u, int ldu, c
     }
 }
 
-// grid (heads * ceil(dv / DELTA_COLS), R), DELTA_COLS * DELTA_LANES threads.  RPL: rows of the state per lane, a multiple of 4
+// grid (heads * ceil(dv / DELTA_COLS), R), DELTA_THREADS threads.  RPL: rows of the state per lane, a multiple of 4
 // (dk <= RPL * DELTA_LANES); lane l of a column holds rows l RPL .. l RPL + RPL - 1, and in shared memory a lane's stretch
-// of k and q is RPL + 4 floats long, so that the eight lanes' 16-byte reads fall into different banks.
+// of k and q is RPL + 4 floats long, so that the 16-byte reads of a quarter warp's lanes fall into different banks.
 //
 // Tokens are taken DELTA_CHUNK at a time, counted from the start of the request's portion.  With S the state before the
 // chunk, P_i the product of the decays up to token i, and w_m = u_m times the decays after token m up to the one at hand,
@@ -140,14 +142,14 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(float* u, int ldu, c
 constexpr int DELTA_CHUNK = 4;
 
 template <int RPL, bool PREPARED>
-__global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(const float* u, int ldu, const float* p, int ldp, int b_col, int a_col,
+__global__ void __launch_bounds__(DELTA_THREADS) gated_delta_kernel(const float* u, int ldu, const float* p, int ldp, int b_col, int a_col,
                                                                               const float* A_log, const float* dt_bias, const float* bg,
                                                                               float* state, const int* q_start, const int* slot_ids, float* o,
                                                                               int H, int G, int dk, int dv) {
     pdl_enter();
-    constexpr int SEG = RPL + 4, KS = DELTA_LANES * SEG, NT = DELTA_COLS * DELTA_LANES, CH = DELTA_CHUNK;
+    constexpr int SEG = RPL + 4, KS = DELTA_LANES * SEG, NT = DELTA_THREADS, CH = DELTA_CHUNK, PER = DELTA_PER, CT = DELTA_COLS / DELTA_PER;
     constexpr int PRE = PREPARED ? DELTA_TILE * DELTA_LANES * RPL / NT : 1;      // k (and q) entries of a tile per thread
-    static_assert(DELTA_TILE % CH == 0 && DELTA_TILE / CH == NT / 32, "one warp per chunk of a tile");
+    static_assert(DELTA_TILE % CH == 0 && NT % 32 == 0 && 2 * DELTA_TILE <= NT, "whole chunks, whole warps, a thread per staged scalar");
     extern __shared__ __align__(16) float sm[];
     float* s_k = sm;                                  // [TILE][KS] unit keys
     float* s_q = s_k + DELTA_TILE * KS;               // [TILE][KS] unit queries times dk^-1/2
@@ -160,16 +162,30 @@ __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(co
     const int head = blockIdx.x / col_blocks, col0 = (blockIdx.x % col_blocks) * DELTA_COLS, r = blockIdx.y;
     const int kvh = head / (H / G);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int sub = threadIdx.x % DELTA_LANES, cl = threadIdx.x / DELTA_LANES, col = col0 + cl;
+    const int sub = threadIdx.x % DELTA_LANES, cl = threadIdx.x / DELTA_LANES;       // the thread's columns: col0 + cl + CT j
     const int first = q_start[r], n = q_start[r + 1] - first;
     const int q_at = kvh * dk, k_at = G * dk + kvh * dk, v_at = 2 * G * dk + head * dv;
     const float decay_rate = PREPARED ? 0.0f : -expf(A_log[head]), bias = PREPARED ? 0.0f : dt_bias[head], q_mult = rsqrtf((float)dk);
-    float* mine = state + (((size_t)slot_ids[r] * H + head) * dv + (col < dv ? col : 0)) * dk;
-    float S[RPL];
+    float* mine = state + ((size_t)slot_ids[r] * H + head) * dv * dk;
+    float S[PER][RPL];
+    const bool by4 = dk % 4 == 0;                     // a column's rows start on 16 bytes: the state moves 16 bytes at a time
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-        const int row = sub * RPL + i;
-        S[i] = col < dv && row < dk ? mine[row] : 0.0f;
+    for (int j = 0; j < PER; ++j) {
+        const int col = col0 + cl + CT * j;
+        if (by4) {
+#pragma unroll
+            for (int i = 0; i < RPL; i += 4) {
+                const int row = sub * RPL + i;
+                const float4 v = col < dv && row < dk ? *reinterpret_cast<const float4*>(mine + (size_t)col * dk + row) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                S[j][i] = v.x, S[j][i + 1] = v.y, S[j][i + 2] = v.z, S[j][i + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                const int row = sub * RPL + i;
+                S[j][i] = col < dv && row < dk ? mine[(size_t)col * dk + row] : 0.0f;
+            }
+        }
     }
     // the padding of the stretches, the rows beyond dk and the tokens beyond a portion read as zero (the products within a
     // chunk are summed over whole stretches)
@@ -228,15 +244,15 @@ __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(co
             }
             __syncthreads();
         }
-        // the products within each chunk: warp c makes those of chunk c (sums over the padded stretches, whose padding is zero)
-        if (warp * CH < nt) {
+        // the products within each chunk, a warp per chunk (sums over the padded stretches, whose padding is zero)
+        for (int cw = warp; cw * CH < nt; cw += nwarps) {
             float kk[CH][CH], kq[CH][CH];
 #pragma unroll
             for (int m = 0; m < CH; ++m)
 #pragma unroll
                 for (int i = 0; i < CH; ++i) kk[m][i] = 0.0f, kq[m][i] = 0.0f;
-            const float* kb = s_k + warp * CH * KS;
-            const float* qb = s_q + warp * CH * KS;
+            const float* kb = s_k + cw * CH * KS;
+            const float* qb = s_q + cw * CH * KS;
             for (int x = lane; x < KS; x += 32) {
                 float kx[CH], qx[CH];
 #pragma unroll
@@ -255,71 +271,91 @@ __global__ void __launch_bounds__(DELTA_COLS* DELTA_LANES) gated_delta_kernel(co
                 for (int i = m; i < CH; ++i) {
                     const float a = warp_sum(kq[m][i]);
                     const float b = i > m ? warp_sum(kk[m][i]) : 0.0f;
-                    if (lane == 0) s_kq[(warp * CH + m) * CH + i] = a, s_kk[(warp * CH + m) * CH + i] = b;
+                    if (lane == 0) s_kq[(cw * CH + m) * CH + i] = a, s_kk[(cw * CH + m) * CH + i] = b;
                 }
         }
         __syncthreads();
         for (int c0 = 0; c0 < nt; c0 += CH) {
             const int cnt = min(CH, nt - c0);
-            float sk[CH], sq[CH];
+            float kreg[CH][RPL], sk[PER][CH], sq[PER][CH];
 #pragma unroll
-            for (int c = 0; c < CH; ++c) sk[c] = 0.0f, sq[c] = 0.0f;
+            for (int j = 0; j < PER; ++j)
+#pragma unroll
+                for (int c = 0; c < CH; ++c) sk[j][c] = 0.0f, sq[j][c] = 0.0f;
 #pragma unroll
             for (int i = 0; i < RPL / 4; ++i) {
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
                     const float4 k4 = reinterpret_cast<const float4*>(s_k + (c0 + c) * KS + sub * SEG)[i];
                     const float4 q4 = reinterpret_cast<const float4*>(s_q + (c0 + c) * KS + sub * SEG)[i];
-                    sk[c] = fmaf(S[4 * i], k4.x, sk[c]), sk[c] = fmaf(S[4 * i + 1], k4.y, sk[c]);
-                    sk[c] = fmaf(S[4 * i + 2], k4.z, sk[c]), sk[c] = fmaf(S[4 * i + 3], k4.w, sk[c]);
-                    sq[c] = fmaf(S[4 * i], q4.x, sq[c]), sq[c] = fmaf(S[4 * i + 1], q4.y, sq[c]);
-                    sq[c] = fmaf(S[4 * i + 2], q4.z, sq[c]), sq[c] = fmaf(S[4 * i + 3], q4.w, sq[c]);
+                    kreg[c][4 * i] = k4.x, kreg[c][4 * i + 1] = k4.y, kreg[c][4 * i + 2] = k4.z, kreg[c][4 * i + 3] = k4.w;
+#pragma unroll
+                    for (int j = 0; j < PER; ++j) {
+                        sk[j][c] = fmaf(S[j][4 * i], k4.x, sk[j][c]), sk[j][c] = fmaf(S[j][4 * i + 1], k4.y, sk[j][c]);
+                        sk[j][c] = fmaf(S[j][4 * i + 2], k4.z, sk[j][c]), sk[j][c] = fmaf(S[j][4 * i + 3], k4.w, sk[j][c]);
+                        sq[j][c] = fmaf(S[j][4 * i], q4.x, sq[j][c]), sq[j][c] = fmaf(S[j][4 * i + 1], q4.y, sq[j][c]);
+                        sq[j][c] = fmaf(S[j][4 * i + 2], q4.z, sq[j][c]), sq[j][c] = fmaf(S[j][4 * i + 3], q4.w, sq[j][c]);
+                    }
                 }
             }
 #pragma unroll
             for (int off = DELTA_LANES / 2; off > 0; off >>= 1) {
 #pragma unroll
-                for (int c = 0; c < CH; ++c) {
-                    sk[c] += __shfl_xor_sync(0xffffffffu, sk[c], off);
-                    sq[c] += __shfl_xor_sync(0xffffffffu, sq[c], off);
-                }
+                for (int j = 0; j < PER; ++j)
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) {
+                        sk[j][c] += __shfl_xor_sync(0xffffffffu, sk[j][c], off);
+                        sq[j][c] += __shfl_xor_sync(0xffffffffu, sq[j][c], off);
+                    }
             }
-            float P = 1.0f, w[CH];
+            float P = 1.0f, w[PER][CH];
 #pragma unroll
             for (int i = 0; i < CH; ++i) {
                 const bool live = i < cnt;
                 const float g = live ? s_g[c0 + i] : 1.0f;
-                float a = P * sk[i], b = P * sq[i];
 #pragma unroll
-                for (int m = 0; m < i; ++m) {
-                    a = fmaf(w[m], s_kk[(c0 + m) * CH + i], a);
-                    b = fmaf(w[m], s_kq[(c0 + m) * CH + i], b);
+                for (int j = 0; j < PER; ++j) {
+                    const int col = col0 + cl + CT * j;
+                    float a = P * sk[j][i], b = P * sq[j][i];
+#pragma unroll
+                    for (int m = 0; m < i; ++m) {
+                        a = fmaf(w[j][m], s_kk[(c0 + m) * CH + i], a);
+                        b = fmaf(w[j][m], s_kq[(c0 + m) * CH + i], b);
+                    }
+                    const float uu = live ? s_beta[c0 + i] * (s_v[(c0 + i) * DELTA_COLS + cl + CT * j] - g * a) : 0.0f;
+                    if (live && sub == 0 && col < dv) o[(size_t)(first + t0 + c0 + i) * H * dv + head * dv + col] = fmaf(s_kq[(c0 + i) * CH + i], uu, g * b);
+#pragma unroll
+                    for (int m = 0; m < i; ++m) w[j][m] *= g;
+                    w[j][i] = uu;
                 }
-                const float uu = live ? s_beta[c0 + i] * (s_v[(c0 + i) * DELTA_COLS + cl] - g * a) : 0.0f;
-                if (live && sub == 0 && col < dv) o[(size_t)(first + t0 + c0 + i) * H * dv + head * dv + col] = fmaf(s_kq[(c0 + i) * CH + i], uu, g * b);
                 P *= g;
-#pragma unroll
-                for (int m = 0; m < i; ++m) w[m] *= g;
-                w[i] = uu;
             }
 #pragma unroll
-            for (int i = 0; i < RPL / 4; ++i) {
-                float acc[4] = {P * S[4 * i], P * S[4 * i + 1], P * S[4 * i + 2], P * S[4 * i + 3]};
+            for (int j = 0; j < PER; ++j)
 #pragma unroll
-                for (int c = 0; c < CH; ++c) {
-                    const float4 k4 = reinterpret_cast<const float4*>(s_k + (c0 + c) * KS + sub * SEG)[i];
-                    acc[0] = fmaf(w[c], k4.x, acc[0]), acc[1] = fmaf(w[c], k4.y, acc[1]);
-                    acc[2] = fmaf(w[c], k4.z, acc[2]), acc[3] = fmaf(w[c], k4.w, acc[3]);
+                for (int i = 0; i < RPL; ++i) {
+                    float acc = P * S[j][i];
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) acc = fmaf(w[j][c], kreg[c][i], acc);
+                    S[j][i] = acc;
                 }
-                S[4 * i] = acc[0], S[4 * i + 1] = acc[1], S[4 * i + 2] = acc[2], S[4 * i + 3] = acc[3];
-            }
         }
     }
-    if (col < dv) {
 #pragma unroll
-        for (int i = 0; i < RPL; ++i) {
-            const int row = sub * RPL + i;
-            if (row < dk) mine[row] = S[i];
+    for (int j = 0; j < PER; ++j) {
+        const int col = col0 + cl + CT * j;
+        if (col < dv && by4) {
+#pragma unroll
+            for (int i = 0; i < RPL; i += 4) {
+                const int row = sub * RPL + i;
+                if (row < dk) *reinterpret_cast<float4*>(mine + (size_t)col * dk + row) = make_float4(S[j][i], S[j][i + 1], S[j][i + 2], S[j][i + 3]);
+            }
+        } else if (col < dv) {
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                const int row = sub * RPL + i;
+                if (row < dk) mine[(size_t)col * dk + row] = S[j][i];
+            }
         }
     }
 }
@@ -386,7 +422,7 @@ Q6K_API int q6k_gated_delta(float* u, int ldu, const float* p, int ldp, int b_co
     const int rpl = ((dk + DELTA_LANES - 1) / DELTA_LANES + 3) / 4 * 4;
     const int RPL_ = rpl <= 4 ? 4 : rpl <= 8 ? 8 : rpl <= 16 ? 16 : 32;
     const size_t smem = (size_t)(2 * DELTA_TILE * DELTA_LANES * (RPL_ + 4) + DELTA_TILE * DELTA_COLS + 2 * DELTA_TILE + 2 * DELTA_TILE * DELTA_CHUNK) * sizeof(float);
-#define Q6K_DELTA_GO(R_, P_) q6k_launch(gated_delta_kernel<R_, P_>, grid, DELTA_COLS * DELTA_LANES, smem, st, u, ldu, p, ldp, b_col, a_col, A_log, dt_bias, bg, state, q_start, slot_ids, o, H, G, dk, dv)
+#define Q6K_DELTA_GO(R_, P_) q6k_launch(gated_delta_kernel<R_, P_>, grid, DELTA_THREADS, smem, st, u, ldu, p, ldp, b_col, a_col, A_log, dt_bias, bg, state, q_start, slot_ids, o, H, G, dk, dv)
     if (bg) {
         if (RPL_ == 4) Q6K_DELTA_GO(4, true);
         else if (RPL_ == 8) Q6K_DELTA_GO(8, true);
