@@ -44,57 +44,27 @@ __device__ __forceinline__ float projected(const float* x, int slices, size_t sl
     return bias ? v + bias[c] : v;
 }
 
-// grid (ceil(T / CONV_ROWS), ceil(copy_to / 256)).  x: FP32 [slices, T, ldx], the convolved channels in its first C columns; the
-// columns from C to `copy_to` pass through (summed, no bias); tail: FP32 [slots, taps-1, C]; out: FP32 [T, ldo].
-// A thread walks CONV_ROWS consecutive rows of the step for one channel with the last taps - 1 projected values in
-// registers, so every value is read (and its slices summed) once; where a row opens another request's portion the
-// window is taken anew from that request's tail.  The taps are added oldest first, whatever the rows' grouping.
-constexpr int CONV_ROWS = 8;
-
+// grid (T, ceil(C / 256)).  x: FP32 [slices, T, ldx], the convolved channels in its first C columns; the columns from C
+// to `copy_to` pass through (summed, no bias); tail: FP32 [slots, taps-1, C]; out: FP32 [T, ldo].
 __global__ void __launch_bounds__(256) short_conv_kernel(const float* x, int slices, size_t slice_stride, int ldx, const float* bias,
                                                          const float* w, const float* tail, const int* req_of_token, const int* q_start,
-                                                         const int* slot_ids, float* out, int ldo, int T_, int C, int copy_to, int taps, int act) {
+                                                         const int* slot_ids, float* out, int ldo, int C, int copy_to, int taps, int act) {
     pdl_enter();
-    const int t0 = blockIdx.x * CONV_ROWS, c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= copy_to) return;
-    const int t_end = min(T_, t0 + CONV_ROWS);
     if (c >= C) {
-        for (int t = t0; t < t_end; ++t) out[(size_t)t * ldo + c] = projected(x, slices, slice_stride, ldx, nullptr, t, c);
+        out[(size_t)t * ldo + c] = projected(x, slices, slice_stride, ldx, nullptr, t, c);
         return;
     }
-    float wv[CONV_MAX_TAPS], win[CONV_MAX_TAPS];          // win[k]: the projected value taps - 1 - k rows back
-#pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) wv[j] = j < taps ? w[(size_t)c * taps + j] : 0.0f;
-    int r = -1;
-    for (int t = t0; t < t_end; ++t) {
-        const int r_now = req_of_token[t];
-        if (r_now != r) {                                    // the block's first row, or the first row of another request's portion
-            r = r_now;
-            const int first = q_start[r], i = t - first;
-            const float* old = tail + (size_t)slot_ids[r] * (taps - 1) * C;
-#pragma unroll
-            for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) {
-                if (k < taps - 1) {
-                    const int src = i - (taps - 1) + k;      // index within the portion; negative: before it
-                    win[k] = src >= 0 ? projected(x, slices, slice_stride, ldx, bias, first + src, c) : old[(size_t)(taps - 1 + src) * C + c];
-                }
-            }
-        }
-        const float cur = projected(x, slices, slice_stride, ldx, bias, t, c);
-        float acc = 0.0f;
-#pragma unroll
-        for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
-            if (k < taps - 1) acc = fmaf(wv[k], win[k], acc);
-#pragma unroll
-        for (int k = 0; k < CONV_MAX_TAPS; ++k)
-            if (k == taps - 1) acc = fmaf(wv[k], cur, acc);
-        out[(size_t)t * ldo + c] = act ? silu_f(acc) : acc;
-#pragma unroll
-        for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) {
-            if (k + 1 < taps - 1) win[k] = win[k + 1];
-            else if (k + 1 == taps - 1) win[k] = cur;
-        }
+    const int r = req_of_token[t], first = q_start[r], i = t - first;
+    const float* old = tail + (size_t)slot_ids[r] * (taps - 1) * C;
+    float acc = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int src = i - (taps - 1 - j);                      // index within the portion; negative: before it
+        const float v = src >= 0 ? projected(x, slices, slice_stride, ldx, bias, first + src, c) : old[(size_t)(taps - 1 + src) * C + c];
+        acc = fmaf(w[(size_t)c * taps + j], v, acc);
     }
+    out[(size_t)t * ldo + c] = act ? silu_f(acc) : acc;
 }
 
 // grid (R, ceil(C / 256)): the slot's tail becomes the last taps - 1 projected values of the request, this step's rows included.
@@ -438,10 +408,10 @@ Q6K_API int q6k_short_conv(const float* x, int slices, long long slice_stride, i
     Q6K_REQUIRE(T_ > 0 && C > 0 && copy_to >= C && taps >= 1 && taps <= CONV_MAX_TAPS && slices >= 1,
                 "short_conv: bad sizes T=%d C=%d taps=%d (at most %d taps) slices=%d", T_, C, taps, CONV_MAX_TAPS, slices);
     Q6K_REQUIRE(ldx >= copy_to && ldo >= copy_to && (act == 0 || act == 1), "short_conv: rows of %d and %d for %d columns, act %d", ldx, ldo, copy_to, act);
-    dim3 grid((T_ + CONV_ROWS - 1) / CONV_ROWS, (copy_to + 255) / 256);
+    dim3 grid(T_, (copy_to + 255) / 256);
     Q6K_REQUIRE(grid.y <= 65535, "short_conv: %d channels exceed the grid limit", copy_to);
     q6k_launch(short_conv_kernel, grid, 256, 0, st, x, slices, (size_t)slice_stride, ldx, bias, w, tail, req_of_token, q_start, slot_ids, out,
-               ldo, T_, C, copy_to, taps, act);
+               ldo, C, copy_to, taps, act);
     return q6k_check_launch("short_conv");
 }
 
